@@ -1,0 +1,42 @@
+"""Shared pytest configuration: markers, import path, golden-fixture loader."""
+import glob
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+def golden_names():
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+
+
+def load_golden(name):
+    """One fixture as a dict of CPU tensors (+ ints K, L and level_start_index)."""
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    d = {k: torch.from_numpy(z[k]) for k in ("value", "shapes", "packed", "grad_out", "out", "grad_value", "grad_packed")}
+    d["K"] = int(z["K"])
+    d["L"] = int(d["shapes"].shape[0])
+    sizes = d["shapes"].prod(1)
+    d["lsi"] = torch.cat((sizes.new_zeros(1), sizes.cumsum(0)[:-1]))
+    return d

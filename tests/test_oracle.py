@@ -1,0 +1,64 @@
+"""Pins the CPU oracle (both restatements) to fixtures produced by the reference itself."""
+import pytest
+import torch
+
+from conftest import golden_names, load_golden
+from oracle import c_oracle, fda_oracle
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_torch_restatement_matches_reference_fixture(name):
+    g = load_golden(name)
+    out, gv, gp = fda_oracle.fused_forward_backward(g["value"], g["shapes"], g["packed"], g["grad_out"], g["K"])
+    assert torch.allclose(out, g["out"], rtol=0, atol=2e-6)
+    assert torch.allclose(gv, g["grad_value"], rtol=1e-5, atol=2e-6)
+    assert torch.allclose(gp, g["grad_packed"], rtol=1e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_torch_restatement_chunked_equals_unchunked(name):
+    g = load_golden(name)
+    a = fda_oracle.fused_forward_backward(g["value"], g["shapes"], g["packed"], g["grad_out"], g["K"], chunk=7)
+    b = fda_oracle.fused_forward_backward(g["value"], g["shapes"], g["packed"], g["grad_out"], g["K"])
+    for x, y in zip(a, b):
+        assert torch.allclose(x, y, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(fda_oracle.fused_forward(g["value"], g["shapes"], g["packed"], g["K"], chunk=5), b[0], atol=2e-6)
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_c_restatement_matches_reference_fixture(name):
+    g = load_golden(name)
+    out = c_oracle.forward(g["value"], g["shapes"], g["lsi"], g["packed"], g["K"])
+    gv, gp = c_oracle.backward(g["value"], g["shapes"], g["lsi"], g["packed"], g["grad_out"], g["K"])
+    # fp32 max-abs bound of the operator's parity contract is 1e-4; the C loops
+    # (double accumulation) sit far inside it.
+    assert (out - g["out"]).abs().max() <= 5e-6
+    assert (gv - g["grad_value"]).abs().max() <= 2e-5
+    scale = g["grad_packed"].abs().max().clamp_min(1.0)
+    assert (gp - g["grad_packed"]).abs().max() <= 2e-5 * scale
+
+
+def test_known_answers():
+    """Closed-form cases (no reference needed): constant volume, voxel centres, zero value."""
+    shapes = torch.tensor([[3, 4, 5]])
+    lsi = torch.zeros(1, dtype=torch.long)
+    B, G, D, K, L, Q = 1, 2, 8, 4, 1, 6
+    N = 60
+    gen = torch.Generator().manual_seed(3)
+    # all sampling points strictly inside [0.5/S, 1-0.5/S]: interpolation weights sum to 1
+    loc = torch.rand(B, Q, G, L, K, 3, generator=gen) * 0.5 + 0.25
+    logits = torch.randn(B, Q, G, L, K, generator=gen)
+    packed = fda_oracle.pack_loc_attn(loc, logits)
+    const = torch.full((B, N, G, D), 2.5)
+    for fwd in (lambda v: fda_oracle.fused_forward(v, shapes, packed, K),
+                lambda v: c_oracle.forward(v, shapes, lsi, packed, K)):
+        assert torch.allclose(fwd(const), torch.full((B, Q, G * D), 2.5), atol=1e-5)
+        assert fwd(torch.zeros(B, N, G, D)).abs().max() == 0
+    # every point on the centre of voxel (z=1,y=2,x=3): out = value[voxel]
+    centre = torch.tensor([(3 + 0.5) / 5, (2 + 0.5) / 4, (1 + 0.5) / 3])
+    loc_c = centre.expand(B, Q, G, L, K, 3).contiguous()
+    packed_c = fda_oracle.pack_loc_attn(loc_c, logits)
+    value = torch.randn(B, N, G, D, generator=gen)
+    want = value[:, (1 * 4 + 2) * 5 + 3].reshape(B, 1, G * D).expand(B, Q, G * D)
+    assert torch.allclose(fda_oracle.fused_forward(value, shapes, packed_c, K), want, atol=1e-5)
+    assert torch.allclose(c_oracle.forward(value, shapes, lsi, packed_c, K), want, atol=1e-5)
