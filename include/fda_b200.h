@@ -1,0 +1,141 @@
+/*
+ * fda_b200.h -- C ABI of the B200 (sm_100a) Flash Deformable 3D Attention kernels.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless its
+ * comment says otherwise; `stream` is a cudaStream_t passed as void*; every
+ * call is asynchronous on that stream and returns an fda_status_t.  The
+ * library keeps no per-call state and allocates no device memory; the caller
+ * provides outputs and (for the backward pass) a workspace.
+ *
+ * Tensor layouts (all dense / contiguous):
+ *   value                 [batch][num_value][num_heads][head_dim]      value_dtype
+ *                         num_value = sum_l D_l*H_l*W_l, level-major, cells (z,y,x) row-major
+ *   spatial_shapes        [num_levels][3] = (D_l, H_l, W_l)            int64, device
+ *   level_start_index     [num_levels]    first cell of each level      int64, device
+ *   sampling_loc_attn     [batch][num_query][num_heads][num_levels*num_points*4]   packed_dtype
+ *                         planar per (b,q,g): num_levels*num_points*3 normalised coordinates
+ *                         (x,y,z per point, level-major) followed by num_levels*num_points raw
+ *                         logits; soft-max over the logits happens inside the operator.
+ *   output / grad_output  [batch][num_query][num_heads*head_dim]       value_dtype
+ *   grad_value            like value                                   value_dtype
+ *   grad_sampling_loc_attn like sampling_loc_attn                      packed_dtype
+ *
+ * Supported envelope: num_levels 1..5, num_points in {4, 8} (as the reference's
+ * launch ladders, csrc/cuda/flash_deform_im2col_cuda.cuh:335-379,548-593),
+ * head_dim a multiple of 16 bytes worth of elements (8 for 16-bit, 4 for fp32) with
+ * head_dim*sizeof(value) <= 512, value_dtype in {f32, f16, bf16}; packed_dtype equal to
+ * value_dtype (the reference's only form) or f32 beside a 16-bit value.
+ */
+#ifndef FDA_B200_H_
+#define FDA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fda_dtype {
+    FDA_DTYPE_F32 = 0,
+    FDA_DTYPE_F16 = 1,
+    FDA_DTYPE_BF16 = 2
+} fda_dtype_t;
+
+typedef enum fda_status {
+    FDA_OK = 0,
+    FDA_ERR_NULL_POINTER = 1,
+    FDA_ERR_BAD_DTYPE = 2,        /* unknown dtype, or a packed/value dtype pair outside the envelope */
+    FDA_ERR_BAD_LEVELS = 3,       /* num_levels outside 1..5 */
+    FDA_ERR_BAD_POINTS = 4,       /* num_points not 4 or 8 */
+    FDA_ERR_BAD_HEAD_DIM = 5,     /* head_dim not a multiple of a 16-byte vector, or head row > 512 bytes */
+    FDA_ERR_BAD_SHAPE = 6,        /* a non-positive dimension, or a tensor too large for the index width */
+    FDA_ERR_IM2COL_STEP = 7,      /* batch % min(batch, im2col_step) != 0 */
+    FDA_ERR_WORKSPACE = 8,        /* workspace missing or smaller than fda_backward_workspace_bytes() */
+    FDA_ERR_MISALIGNED = 9,       /* a tensor base address is not 16-byte aligned */
+    FDA_ERR_CUDA = 10,            /* a CUDA runtime call or the kernel launch failed; see fda_last_cuda_error() */
+    FDA_ERR_TOO_LARGE_STATIC = 11 /* problem exceeds a compiled-in capacity */
+} fda_status_t;
+
+/* Human-readable name of a status code (static storage, never NULL). */
+const char *fda_status_string(int status);
+
+/* cudaError_t (as int) of the last failing CUDA call made by this library on the calling thread. */
+int fda_last_cuda_error(void);
+
+/* ABI version: major*1000 + minor. */
+int fda_version(void);
+
+/*
+ * Forward:  output[b,q,g,:] = sum_i softmax(logits)_i * trilinear(value[b, level(i)], loc_i)[g,:]
+ *
+ * Replaces the reference launcher flash_deformable_im2col_cuda(stream, data_value,
+ * data_spatial_shapes, data_level_start_index, data_sampling_loc_attn, data_col, batch_size,
+ * spatial_size, num_heads, channels, num_levels, num_query, num_point, d_stride, block_thread,
+ * use_reg) -- csrc/cuda/flash_deform_im2col_cuda.cuh:548-593 -- and the chunk loop around it in
+ * flash_deform_attn_cuda_forward, csrc/cuda/flash_deform_attn_cuda.cu:46-88.
+ *
+ * im2col_step is validated exactly as there (batch % min(batch, im2col_step) == 0) and otherwise
+ * unused: the whole batch is one launch.  d_stride and block_thread are the reference's launch
+ * hints; they are accepted and ignored.  use_reg != 0 lets the library choose between its
+ * register-staged and shared-memory-staged kernels per shape; use_reg == 0 forces the
+ * shared-memory-staged kernel (the reference's meaning of the flag).
+ * Every element of output is written (no pre-zeroing needed).
+ */
+int fda_forward(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                const void *sampling_loc_attn, void *output,
+                int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                int num_query, int num_points, int value_dtype, int packed_dtype,
+                int im2col_step, int d_stride, int block_thread, int use_reg, void *stream);
+
+/*
+ * Bytes of device workspace fda_backward needs for this problem (0 for an fp32 value: the
+ * scatter then accumulates straight into grad_value).  For 16-bit values it is the fp32
+ * accumulation image of grad_value, batch*num_value*num_heads*head_dim*4 bytes.
+ */
+size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int value_dtype);
+
+/*
+ * Backward: grad_value (scatter-add of softmax_i * w_corner * grad_output through fp32 vector
+ * reductions, then one cast pass for 16-bit values) and grad_sampling_loc_attn (coordinate
+ * gradients and gradients w.r.t. the raw logits, written once each in packed_dtype).
+ *
+ * Replaces flash_deformable_col2im_cuda(stream, data_value, data_spatial_shapes,
+ * data_level_start_index, data_sampling_loc_attn, grad_output, batch_size, spatial_size, num_heads,
+ * channels, num_levels, num_query, num_point, grad_value, grad_sampling_loc, d_stride,
+ * block_thread) -- csrc/cuda/flash_deform_col2im_cuda.cuh:689-731 -- together with the zero-fill,
+ * chunk loop and cast-back of flash_deform_attn_cuda_backward, csrc/cuda/flash_deform_attn_cuda.cu:125-178.
+ *
+ * The library zero-fills what it accumulates into (workspace, or grad_value for fp32); both
+ * outputs are fully written.  workspace must be 16-byte aligned and at least
+ * fda_backward_workspace_bytes() long; it may be NULL when that is 0.
+ */
+int fda_backward(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                 const void *sampling_loc_attn, const void *grad_output,
+                 void *grad_value, void *grad_sampling_loc_attn,
+                 void *workspace, size_t workspace_bytes,
+                 int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                 int num_query, int num_points, int value_dtype, int packed_dtype,
+                 int im2col_step, int d_stride, int block_thread, void *stream);
+
+/*
+ * The two halves of fda_backward for callers that reduce the fp32 accumulation image across
+ * devices before the cast (queries sharded over GPUs, value replicated): fda_backward_accumulate
+ * zero-fills `accum` (fp32, value's shape) and scatter-adds into it, and writes
+ * grad_sampling_loc_attn; fda_cast_grad_value converts an fp32 image to value_dtype.
+ * Between the two the caller may sum `accum` over ranks.  No counterpart in the reference (it
+ * has no multi-device path); semantics are those of fda_backward split at the cast.
+ */
+int fda_backward_accumulate(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                            const void *sampling_loc_attn, const void *grad_output,
+                            float *accum, void *grad_sampling_loc_attn,
+                            int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                            int num_query, int num_points, int value_dtype, int packed_dtype,
+                            int im2col_step, void *stream);
+
+int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_elements, int value_dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FDA_B200_H_ */

@@ -1,0 +1,132 @@
+"""ctypes view of the C ABI in ``include/fda_b200.h`` (``libfda_b200.so``), for callers that hold raw
+device buffers: the parity tests, the benchmark and the multi-GPU wrapper.  Tensors are only used
+here as owners of device memory; the library sees pointers, sizes and a stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfda_b200.so")
+
+DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+EXPORTS = (
+    "fda_status_string", "fda_last_cuda_error", "fda_version", "fda_forward",
+    "fda_backward_workspace_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
+)
+
+_lib = None
+
+
+class FdaError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"fda status {status}: {message}")
+        self.status = status
+
+
+def load() -> ctypes.CDLL:
+    """Loads the library; raises if it has not been built (there is no fallback)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f"{LIB_PATH} not built; run `python -m ops3d_b200.build`")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    lib.fda_status_string.argtypes = [i]
+    lib.fda_status_string.restype = ctypes.c_char_p
+    lib.fda_last_cuda_error.restype = i
+    lib.fda_version.restype = i
+    lib.fda_forward.argtypes = [vp] * 5 + [i] * 13 + [vp]
+    lib.fda_forward.restype = i
+    lib.fda_backward_workspace_bytes.argtypes = [i] * 5
+    lib.fda_backward_workspace_bytes.restype = sz
+    lib.fda_backward.argtypes = [vp] * 8 + [sz] + [i] * 12 + [vp]
+    lib.fda_backward.restype = i
+    lib.fda_backward_accumulate.argtypes = [vp] * 7 + [i] * 10 + [vp]
+    lib.fda_backward_accumulate.restype = i
+    lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
+    lib.fda_cast_grad_value.restype = i
+    _lib = lib
+    return lib
+
+
+def check(status: int):
+    if status != 0:
+        msg = load().fda_status_string(status).decode()
+        if status == 10:
+            msg += f" (cudaError {load().fda_last_cuda_error()})"
+        raise FdaError(status, msg)
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dims(value, shapes, packed):
+    B, N, G, D = value.shape
+    return B, N, G, D, shapes.shape[0], packed.shape[1]
+
+
+def forward(value, shapes, lsi, packed, K, im2col_step=64, use_reg=True, out=None):
+    """``fda_forward`` on CUDA tensors; returns ``[B, Q, G*D]`` in ``value.dtype``."""
+    B, N, G, D, L, Q = _dims(value, shapes, packed)
+    if out is None:
+        out = torch.empty(B, Q, G * D, dtype=value.dtype, device=value.device)
+    with torch.cuda.device(value.device):
+        check(load().fda_forward(
+            value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), out.data_ptr(),
+            B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype],
+            im2col_step, 8, 0, int(bool(use_reg)), _stream(value)))
+    return out
+
+
+def workspace_bytes(value) -> int:
+    B, N, G, D = value.shape
+    return int(load().fda_backward_workspace_bytes(B, N, G, D, DTYPE_CODE[value.dtype]))
+
+
+def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value=None, grad_packed=None,
+             workspace=None):
+    """``fda_backward`` on CUDA tensors; returns ``(grad_value, grad_packed)``."""
+    B, N, G, D, L, Q = _dims(value, shapes, packed)
+    if grad_value is None:
+        grad_value = torch.empty_like(value)
+    if grad_packed is None:
+        grad_packed = torch.empty_like(packed)
+    need = workspace_bytes(value)
+    if need and workspace is None:
+        workspace = torch.empty(need // 4, dtype=torch.float32, device=value.device)
+    with torch.cuda.device(value.device):
+        check(load().fda_backward(
+            value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
+            grad_value.data_ptr(), grad_packed.data_ptr(),
+            workspace.data_ptr() if workspace is not None else None,
+            workspace.numel() * workspace.element_size() if workspace is not None else 0,
+            B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype],
+            im2col_step, 1, 0, _stream(value)))
+    return grad_value, grad_packed
+
+
+def backward_accumulate(value, shapes, lsi, packed, grad_out, K, accum, grad_packed=None, im2col_step=64):
+    """``fda_backward_accumulate``: zero-fills and fills the fp32 image ``accum``; returns ``grad_packed``."""
+    B, N, G, D, L, Q = _dims(value, shapes, packed)
+    if grad_packed is None:
+        grad_packed = torch.empty_like(packed)
+    with torch.cuda.device(value.device):
+        check(load().fda_backward_accumulate(
+            value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
+            accum.data_ptr(), grad_packed.data_ptr(),
+            B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype], im2col_step, _stream(value)))
+    return grad_packed
+
+
+def cast_grad_value(accum, grad_value):
+    with torch.cuda.device(accum.device):
+        check(load().fda_cast_grad_value(accum.data_ptr(), grad_value.data_ptr(), accum.numel(),
+                                         DTYPE_CODE[grad_value.dtype], _stream(accum)))
+    return grad_value

@@ -1,0 +1,133 @@
+// Thin torch binding over the C ABI of include/fda_b200.h.
+//
+// Exposes, positional-only like the reference's module (csrc/vision.cpp:23-24):
+//   flash_deform_attn_forward (value, spatial_shapes, level_start_index, sampling_loc_attn,
+//                              im2col_step, K, d_stride, block_thread, use_reg) -> Tensor[B,Lq,G*D]
+//   flash_deform_attn_backward(value, spatial_shapes, level_start_index, sampling_loc_attn,
+//                              grad_output, im2col_step, K, d_stride, block_thread)
+//                              -> [grad_value[B,N,G,D], grad_sampling_loc_attn[B,Lq,G,L*K*4]]
+// with the argument meaning and error behaviour of csrc/flash_deform_attn.h:7-52 and
+// csrc/cuda/flash_deform_attn_cuda.cu:20-179: RuntimeError for CPU / non-contiguous tensors and
+// for batch % min(batch, im2col_step) != 0, ValueError for an unsupported level or point count.
+// This file only checks tensors, allocates outputs from torch's allocator, and forwards raw
+// pointers plus the current CUDA stream; all arithmetic lives behind the C ABI.
+#include <torch/extension.h>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/fda_b200.h"
+
+namespace {
+
+int dtype_code(const at::Tensor &t, const char *name) {
+    switch (t.scalar_type()) {
+        case at::kFloat: return FDA_DTYPE_F32;
+        case at::kHalf: return FDA_DTYPE_F16;
+        case at::kBFloat16: return FDA_DTYPE_BF16;
+        default: TORCH_CHECK(false, name, " must be float32, float16 or bfloat16, got ", t.scalar_type());
+    }
+    return -1;
+}
+
+void check_cuda_contiguous(const at::Tensor &t, const char *name) {
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (this operator has no CPU implementation)");
+    TORCH_CHECK(t.is_contiguous(), name, " tensor has to be contiguous");
+}
+
+void raise_status(int status, const char *what) {
+    if (status == FDA_OK) return;
+    std::string msg = std::string(what) + ": " + fda_status_string(status);
+    if (status == FDA_ERR_CUDA) msg += std::string(" (") + cudaGetErrorString((cudaError_t)fda_last_cuda_error()) + ")";
+    // the reference raises std::invalid_argument (-> ValueError) for level / point counts outside its ladders
+    if (status == FDA_ERR_BAD_LEVELS || status == FDA_ERR_BAD_POINTS) throw std::invalid_argument(msg);
+    TORCH_CHECK(false, msg);
+}
+
+struct Dims {
+    int B, N, G, D, L, Q;
+};
+
+Dims check_common(const at::Tensor &value, const at::Tensor &spatial_shapes, const at::Tensor &level_start_index,
+                  const at::Tensor &sampling_loc_attn, int K) {
+    check_cuda_contiguous(value, "value");
+    check_cuda_contiguous(spatial_shapes, "spatial_shapes");
+    check_cuda_contiguous(level_start_index, "level_start_index");
+    check_cuda_contiguous(sampling_loc_attn, "sampling_loc_attn");
+    TORCH_CHECK(value.dim() == 4, "value must be [B, N, G, D]");
+    TORCH_CHECK(sampling_loc_attn.dim() == 4, "sampling_loc_attn must be [B, Lq, G, L*K*4]");
+    TORCH_CHECK(spatial_shapes.dim() == 2 && spatial_shapes.size(1) == 3, "spatial_shapes must be [L, 3]");
+    TORCH_CHECK(spatial_shapes.scalar_type() == at::kLong && level_start_index.scalar_type() == at::kLong,
+                "spatial_shapes and level_start_index must be int64");
+    TORCH_CHECK(level_start_index.numel() == spatial_shapes.size(0), "level_start_index must have one entry per level");
+    TORCH_CHECK(value.device() == sampling_loc_attn.device() && value.device() == spatial_shapes.device() &&
+                    value.device() == level_start_index.device(),
+                "all tensors must be on the same device");
+    Dims d;
+    d.B = (int)value.size(0); d.N = (int)value.size(1); d.G = (int)value.size(2); d.D = (int)value.size(3);
+    d.L = (int)spatial_shapes.size(0);
+    d.Q = (int)sampling_loc_attn.size(1);
+    TORCH_CHECK(sampling_loc_attn.size(0) == d.B && sampling_loc_attn.size(2) == d.G,
+                "sampling_loc_attn batch / head dimensions do not match value");
+    TORCH_CHECK(sampling_loc_attn.size(3) == (int64_t)d.L * K * 4, "sampling_loc_attn last dimension (",
+                sampling_loc_attn.size(3), ") does not match L*K*4 = ", (int64_t)d.L * K * 4);
+    return d;
+}
+
+at::Tensor flash_deform_attn_forward(const at::Tensor &value, const at::Tensor &spatial_shapes,
+                                     const at::Tensor &level_start_index, const at::Tensor &sampling_loc_attn,
+                                     const int im2col_step, const int K, const int d_stride, const int block_thread,
+                                     const bool use_reg) {
+    const Dims d = check_common(value, spatial_shapes, level_start_index, sampling_loc_attn, K);
+    const int vdt = dtype_code(value, "value"), pdt = dtype_code(sampling_loc_attn, "sampling_loc_attn");
+    c10::cuda::CUDAGuard guard(value.device());
+    if (d.Q == 0 || d.B == 0) return at::zeros({d.B, d.Q, d.G * d.D}, value.options());
+    at::Tensor output = at::empty({d.B, d.Q, d.G * d.D}, value.options());
+    const int rc = fda_forward(value.data_ptr(), spatial_shapes.data_ptr<int64_t>(), level_start_index.data_ptr<int64_t>(),
+                               sampling_loc_attn.data_ptr(), output.data_ptr(), d.B, d.N, d.G, d.D, d.L, d.Q, K, vdt, pdt,
+                               im2col_step, d_stride, block_thread, use_reg ? 1 : 0,
+                               at::cuda::getCurrentCUDAStream().stream());
+    raise_status(rc, "flash_deform_attn_forward");
+    return output;
+}
+
+std::vector<at::Tensor> flash_deform_attn_backward(const at::Tensor &value, const at::Tensor &spatial_shapes,
+                                                   const at::Tensor &level_start_index,
+                                                   const at::Tensor &sampling_loc_attn, const at::Tensor &grad_output,
+                                                   const int im2col_step, const int K, const int d_stride,
+                                                   const int block_thread) {
+    const Dims d = check_common(value, spatial_shapes, level_start_index, sampling_loc_attn, K);
+    check_cuda_contiguous(grad_output, "grad_output");
+    TORCH_CHECK(grad_output.scalar_type() == value.scalar_type(), "grad_output must have the dtype of value");
+    TORCH_CHECK(grad_output.numel() == (int64_t)d.B * d.Q * d.G * d.D, "grad_output must be [B, Lq, G*D]");
+    const int vdt = dtype_code(value, "value"), pdt = dtype_code(sampling_loc_attn, "sampling_loc_attn");
+    c10::cuda::CUDAGuard guard(value.device());
+    if (d.Q == 0 || d.B == 0) return {at::zeros_like(value), at::zeros_like(sampling_loc_attn)};
+    at::Tensor grad_value = at::empty_like(value);
+    at::Tensor grad_packed = at::empty_like(sampling_loc_attn);
+    const size_t ws_bytes = fda_backward_workspace_bytes(d.B, d.N, d.G, d.D, vdt);
+    at::Tensor workspace;
+    void *ws_ptr = nullptr;
+    if (ws_bytes > 0) {
+        workspace = at::empty({(int64_t)(ws_bytes / sizeof(float))}, value.options().dtype(at::kFloat));
+        ws_ptr = workspace.data_ptr();
+    }
+    const int rc = fda_backward(value.data_ptr(), spatial_shapes.data_ptr<int64_t>(), level_start_index.data_ptr<int64_t>(),
+                                sampling_loc_attn.data_ptr(), grad_output.data_ptr(), grad_value.data_ptr(),
+                                grad_packed.data_ptr(), ws_ptr, ws_bytes, d.B, d.N, d.G, d.D, d.L, d.Q, K, vdt, pdt,
+                                im2col_step, d_stride, block_thread, at::cuda::getCurrentCUDAStream().stream());
+    raise_status(rc, "flash_deform_attn_backward");
+    return {grad_value, grad_packed};
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "B200 Flash Deformable 3D Attention (torch binding over the fda_b200 C ABI)";
+    m.def("flash_deform_attn_forward", &flash_deform_attn_forward, "Flash Deformable 3D Attention forward (sm_100a)");
+    m.def("flash_deform_attn_backward", &flash_deform_attn_backward, "Flash Deformable 3D Attention backward (sm_100a)");
+}

@@ -1,0 +1,270 @@
+// Host side of the C ABI declared in include/fda_b200.h: argument validation, dtype
+// dispatch and kernel launches.  No torch types, no allocation, nothing but the CUDA runtime.
+#include "../../include/fda_b200.h"
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <set>
+#include <utility>
+
+#include "fda_backward.cuh"
+#include "fda_forward.cuh"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+inline int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return FDA_ERR_CUDA;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int dtype_size(int dt) { return dt == FDA_DTYPE_F32 ? 4 : 2; }
+
+struct Shape {
+    int B, N, G, D, L, Q, K, vdt, pdt;
+};
+
+int validate(const Shape &s, int im2col_step) {
+    if (s.vdt < 0 || s.vdt > 2 || s.pdt < 0 || s.pdt > 2) return FDA_ERR_BAD_DTYPE;
+    if (!(s.pdt == s.vdt || (s.pdt == FDA_DTYPE_F32))) return FDA_ERR_BAD_DTYPE;
+    if (s.B <= 0 || s.N <= 0 || s.G <= 0 || s.D <= 0 || s.Q <= 0) return FDA_ERR_BAD_SHAPE;
+    if (s.L < 1 || s.L > fda::kMaxLevels) return FDA_ERR_BAD_LEVELS;
+    if (s.K != 4 && s.K != 8) return FDA_ERR_BAD_POINTS;
+    const int cpl = 16 / dtype_size(s.vdt);
+    if (s.D % cpl != 0 || s.D / cpl > 32) return FDA_ERR_BAD_HEAD_DIM;
+    // 32-bit element offsets inside one batch element; 32-bit row index; grid.y limit
+    if ((int64_t)s.N * s.G * s.D >= (int64_t)1 << 31) return FDA_ERR_BAD_SHAPE;
+    if ((int64_t)s.Q * s.G >= (int64_t)1 << 31) return FDA_ERR_BAD_SHAPE;
+    if (s.B > 65535) return FDA_ERR_BAD_SHAPE;
+    const int step = s.B < im2col_step ? s.B : im2col_step;
+    if (step <= 0 || s.B % step != 0) return FDA_ERR_IM2COL_STEP;
+    return FDA_OK;
+}
+
+fda::Problem make_problem(const Shape &s) {
+    fda::Problem p;
+    std::memset(&p, 0, sizeof(p));
+    p.B = s.B; p.N = s.N; p.G = s.G; p.D = s.D; p.L = s.L; p.K = s.K; p.Q = s.Q;
+    p.LK = s.L * s.K;
+    p.k_shift = s.K == 8 ? 1 : 0;
+    p.lpg = s.D / (16 / dtype_size(s.vdt));
+    int lg = 0;
+    while ((1 << lg) < p.lpg) ++lg;
+    p.gs_log2 = lg;
+    p.rows_per_b = s.Q * s.G;
+    p.GD = s.G * s.D;
+    return p;
+}
+
+// Row stride (floats) of a staged tile holding `floats_per_row` payload floats: a multiple of 4
+// (16-byte vector access) whose quarter is odd, so that the rows of a warp start in different banks.
+inline int padded_stride(int floats_per_row) {
+    int s = (floats_per_row + 3) & ~3;
+    if (((s >> 2) & 1) == 0) s += 4;
+    return s;
+}
+
+// Opt in to > 48 KB of dynamic shared memory, once per (device, kernel).
+int ensure_smem(const void *kernel, size_t bytes) {
+    static std::mutex mu;
+    static std::set<std::pair<int, const void *>> done;
+    if (bytes <= 48 * 1024) return FDA_OK;
+    if (bytes > 200 * 1024) return FDA_ERR_TOO_LARGE_STATIC;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.count({dev, kernel})) return FDA_OK;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return cuda_fail(e);
+    done.insert({dev, kernel});
+    return FDA_OK;
+}
+
+// Threads per block: 256 unless the staged tile of 256 threads' rows would leave room for fewer
+// than two blocks per SM; then halve (down to one warp).  Rows never straddle blocks.
+inline int pick_threads(const fda::Problem &p, int row_stride) {
+    int threads = fda::kThreads;
+    while (threads > 32 && (size_t)(threads >> p.gs_log2) * row_stride * sizeof(float) > 96 * 1024) threads >>= 1;
+    return threads;
+}
+
+inline dim3 row_grid(const fda::Problem &p, int threads) {
+    const int rows_per_block = threads >> p.gs_log2;
+    return dim3((unsigned)((p.rows_per_b + rows_per_block - 1) / rows_per_block), (unsigned)p.B, 1);
+}
+
+// 0: let the library choose, 1: register-staged, 2: shared-memory-staged
+int forced_forward_variant() {
+    const char *e = std::getenv("FDA_FORCE_VARIANT");
+    if (!e) return 0;
+    if (!std::strcmp(e, "reg")) return 1;
+    if (!std::strcmp(e, "smem")) return 2;
+    return 0;
+}
+
+template <typename VT, typename PT>
+int launch_forward(fda::Problem p, bool stage, cudaStream_t st) {
+    if (stage) {
+        p.row_stride = padded_stride(4 * p.LK);
+        const int threads = pick_threads(p, p.row_stride);
+        const size_t smem = (size_t)(threads >> p.gs_log2) * p.row_stride * sizeof(float);
+        auto kern = fda::fda_forward_kernel<VT, PT, true>;
+        if (int rc = ensure_smem(reinterpret_cast<const void *>(kern), smem)) return rc;
+        kern<<<row_grid(p, threads), threads, smem, st>>>(p);
+    } else {
+        fda::fda_forward_kernel<VT, PT, false><<<row_grid(p, fda::kThreads), fda::kThreads, 0, st>>>(p);
+    }
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FDA_OK : cuda_fail(e);
+}
+
+template <typename VT, typename PT>
+int launch_backward(fda::Problem p, cudaStream_t st) {
+    p.row_stride = padded_stride(5 * p.LK);
+    const int threads = pick_threads(p, p.row_stride);
+    const size_t smem = (size_t)(threads >> p.gs_log2) * p.row_stride * sizeof(float);
+    auto kern = fda::fda_backward_kernel<VT, PT>;
+    if (int rc = ensure_smem(reinterpret_cast<const void *>(kern), smem)) return rc;
+    kern<<<row_grid(p, threads), threads, smem, st>>>(p);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FDA_OK : cuda_fail(e);
+}
+
+#define FDA_DISPATCH(vdt, pdt, CALL)                                                         \
+    [&]() -> int {                                                                           \
+        if (vdt == FDA_DTYPE_F32) { using VT = float; using PT = float; return CALL; }       \
+        if (vdt == FDA_DTYPE_F16 && pdt == FDA_DTYPE_F16) { using VT = __half; using PT = __half; return CALL; } \
+        if (vdt == FDA_DTYPE_F16) { using VT = __half; using PT = float; return CALL; }      \
+        if (pdt == FDA_DTYPE_BF16) { using VT = __nv_bfloat16; using PT = __nv_bfloat16; return CALL; } \
+        { using VT = __nv_bfloat16; using PT = float; return CALL; }                         \
+    }()
+
+}  // namespace
+
+extern "C" {
+
+const char *fda_status_string(int status) {
+    switch (status) {
+        case FDA_OK: return "ok";
+        case FDA_ERR_NULL_POINTER: return "null pointer argument";
+        case FDA_ERR_BAD_DTYPE: return "unsupported dtype (value f32/f16/bf16; packed equal to value, or f32)";
+        case FDA_ERR_BAD_LEVELS: return "num_levels must be in 1..5";
+        case FDA_ERR_BAD_POINTS: return "num_points must be 4 or 8";
+        case FDA_ERR_BAD_HEAD_DIM: return "head_dim must be a multiple of a 16-byte vector and at most 512 bytes";
+        case FDA_ERR_BAD_SHAPE: return "non-positive or too large dimension";
+        case FDA_ERR_IM2COL_STEP: return "batch must divide im2col_step";
+        case FDA_ERR_WORKSPACE: return "workspace missing or too small";
+        case FDA_ERR_MISALIGNED: return "tensor base address not 16-byte aligned";
+        case FDA_ERR_CUDA: return "CUDA runtime error";
+        case FDA_ERR_TOO_LARGE_STATIC: return "problem exceeds a compiled-in capacity";
+        default: return "unknown status";
+    }
+}
+
+int fda_last_cuda_error(void) { return g_last_cuda_error; }
+
+int fda_version(void) { return 1000; }
+
+int fda_forward(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                const void *sampling_loc_attn, void *output,
+                int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                int num_query, int num_points, int value_dtype, int packed_dtype,
+                int im2col_step, int d_stride, int block_thread, int use_reg, void *stream) {
+    (void)d_stride; (void)block_thread;
+    if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !output) return FDA_ERR_NULL_POINTER;
+    const Shape s{batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, packed_dtype};
+    if (int rc = validate(s, im2col_step)) return rc;
+    if (!aligned16(value) || !aligned16(sampling_loc_attn) || !aligned16(output)) return FDA_ERR_MISALIGNED;
+    fda::Problem p = make_problem(s);
+    p.value = value; p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn; p.out = output;
+    // Staging choice per shape: with several rows per warp the packed rows of a warp are one
+    // contiguous span, which the staged kernel reads with full-width coalesced loads.
+    bool stage = !use_reg || p.gs_log2 <= 3;
+    const int forced = forced_forward_variant();
+    if (forced == 1 && use_reg) stage = false;
+    if (forced == 2) stage = true;
+    return FDA_DISPATCH(value_dtype, packed_dtype, (launch_forward<VT, PT>(p, stage, static_cast<cudaStream_t>(stream))));
+}
+
+size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int value_dtype) {
+    if (value_dtype == FDA_DTYPE_F32) return 0;
+    if (batch <= 0 || num_value <= 0 || num_heads <= 0 || head_dim <= 0) return 0;
+    return (size_t)batch * num_value * num_heads * head_dim * sizeof(float);
+}
+
+int fda_backward_accumulate(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                            const void *sampling_loc_attn, const void *grad_output,
+                            float *accum, void *grad_sampling_loc_attn,
+                            int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                            int num_query, int num_points, int value_dtype, int packed_dtype,
+                            int im2col_step, void *stream) {
+    if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !grad_output || !accum || !grad_sampling_loc_attn)
+        return FDA_ERR_NULL_POINTER;
+    const Shape s{batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, packed_dtype};
+    if (int rc = validate(s, im2col_step)) return rc;
+    if (!aligned16(value) || !aligned16(sampling_loc_attn) || !aligned16(grad_output) || !aligned16(accum) ||
+        !aligned16(grad_sampling_loc_attn))
+        return FDA_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t n = (size_t)batch * num_value * num_heads * head_dim;
+    cudaError_t e = cudaMemsetAsync(accum, 0, n * sizeof(float), st);
+    if (e != cudaSuccess) return cuda_fail(e);
+    fda::Problem p = make_problem(s);
+    p.value = value; p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn;
+    p.grad_out = grad_output; p.accum = accum; p.grad_packed = grad_sampling_loc_attn;
+    return FDA_DISPATCH(value_dtype, packed_dtype, (launch_backward<VT, PT>(p, st)));
+}
+
+int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_elements, int value_dtype, void *stream) {
+    if (!accum || !grad_value) return FDA_ERR_NULL_POINTER;
+    if (value_dtype < 0 || value_dtype > 2) return FDA_ERR_BAD_DTYPE;
+    if (num_elements % 4 != 0) return FDA_ERR_BAD_SHAPE;
+    if (!aligned16(accum) || !aligned16(grad_value)) return FDA_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaSuccess;
+    if (value_dtype == FDA_DTYPE_F32) {
+        if (static_cast<const void *>(accum) != grad_value)
+            e = cudaMemcpyAsync(grad_value, accum, num_elements * sizeof(float), cudaMemcpyDeviceToDevice, st);
+        return e == cudaSuccess ? FDA_OK : cuda_fail(e);
+    }
+    const size_t n4 = num_elements / 4;
+    if (n4 == 0) return FDA_OK;
+    size_t blocks = (n4 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;  // grid-stride; 16 resident blocks of 256 threads cover an SM
+    if (value_dtype == FDA_DTYPE_F16)
+        fda::fda_cast_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(accum, static_cast<__half *>(grad_value), n4);
+    else
+        fda::fda_cast_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(accum, static_cast<__nv_bfloat16 *>(grad_value), n4);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? FDA_OK : cuda_fail(e);
+}
+
+int fda_backward(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                 const void *sampling_loc_attn, const void *grad_output,
+                 void *grad_value, void *grad_sampling_loc_attn,
+                 void *workspace, size_t workspace_bytes,
+                 int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                 int num_query, int num_points, int value_dtype, int packed_dtype,
+                 int im2col_step, int d_stride, int block_thread, void *stream) {
+    (void)d_stride; (void)block_thread;
+    if (!grad_value) return FDA_ERR_NULL_POINTER;
+    const size_t need = fda_backward_workspace_bytes(batch, num_value, num_heads, head_dim, value_dtype);
+    float *accum = static_cast<float *>(grad_value);
+    if (need > 0) {
+        if (!workspace || workspace_bytes < need) return FDA_ERR_WORKSPACE;
+        accum = static_cast<float *>(workspace);
+    }
+    if (!aligned16(grad_value)) return FDA_ERR_MISALIGNED;
+    int rc = fda_backward_accumulate(value, spatial_shapes, level_start_index, sampling_loc_attn, grad_output, accum,
+                                     grad_sampling_loc_attn, batch, num_value, num_heads, head_dim, num_levels,
+                                     num_query, num_points, value_dtype, packed_dtype, im2col_step, stream);
+    if (rc != FDA_OK || need == 0) return rc;
+    return fda_cast_grad_value(accum, grad_value, (size_t)batch * num_value * num_heads * head_dim, value_dtype, stream);
+}
+
+}  // extern "C"

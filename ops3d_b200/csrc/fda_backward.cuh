@@ -1,0 +1,203 @@
+// Backward kernels of Flash Deformable 3D Attention for sm_100a.
+//
+// Replaces backward_kernel_warp_primitive / backward_kernel of the reference
+// (csrc/cuda/flash_deform_col2im_cuda.cuh:248-429 and :50-244) and its trilinear
+// helper (csrc/cuda/common.h:141-354):
+//   * each warp stages the packed rows it owns into a private shared-memory tile
+//     (coalesced), and at the end writes the finished gradient rows back from the
+//     same tile (coalesced, already in the packed dtype) -- no fp32 copy of
+//     grad_sampling_loc_attn, no later cast pass, no block barrier in the loop;
+//   * per point: 8 predicated 16-byte corner loads, per-corner dot products with
+//     grad_output, the four partial sums (d/dx, d/dy, d/dz, d/d alpha) reduced over
+//     the lanes of the row with xor-shuffles;
+//   * grad_value: fp32 scatter with red.global.add.v4.f32 (one 16-byte reduction per
+//     lane and corner half), channels interleaved over the lanes of a row so that one
+//     warp instruction covers whole 32-byte sectors of the accumulation image;
+//   * soft-max backward in closed form, grad_logit_i = p_i * (dalpha_i - sum_j p_j dalpha_j),
+//     instead of the reference's O((L*K)^2) Jacobian loop (:413-427).
+#pragma once
+
+#include "fda_device.cuh"
+
+namespace fda {
+
+template <typename VT, typename PT>
+__global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem p) {
+    constexpr int CPL = Vec16<VT>::kCPL;
+    constexpr int NRED = CPL / 4;  // 16-byte fp32 reductions per lane and corner
+    __shared__ LevelGeom geom[kMaxLevels];
+    extern __shared__ __align__(16) float smem_tile[];
+
+    const int tid = threadIdx.x;
+    if (tid < p.L) {
+        LevelGeom lv;
+        lv.D = (int)p.shapes[3 * tid];
+        lv.H = (int)p.shapes[3 * tid + 1];
+        lv.W = (int)p.shapes[3 * tid + 2];
+        lv.start = (int)p.lsi[tid];
+        geom[tid] = lv;
+    }
+
+    const int b = blockIdx.y;
+    const int gs = 1 << p.gs_log2;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int lane_c = tid & (gs - 1);
+    const int rows_per_block = (int)blockDim.x >> p.gs_log2;
+    const int rows_per_warp = 32 >> p.gs_log2;
+    const int row = blockIdx.x * rows_per_block + (tid >> p.gs_log2);  // q * G + g inside batch element b
+    const bool row_ok = row < p.rows_per_b;
+    const bool active = row_ok && lane_c < p.lpg;
+    const int LK = p.LK;
+
+    // Tile row layout (fp32): [0,3LK) coordinates -> coordinate gradients,
+    // [3LK,4LK) logits -> dalpha -> logit gradients, [4LK,5LK) exp(logit - max).
+    const int first = blockIdx.x * rows_per_block + warp * rows_per_warp;
+    float *wtile = smem_tile + warp * rows_per_warp * p.row_stride;
+    int nrows = p.rows_per_b - first;
+    nrows = nrows < 0 ? 0 : (nrows > rows_per_warp ? rows_per_warp : nrows);
+    const size_t warp_elem0 = ((size_t)b * p.rows_per_b + first) * (size_t)(4 * LK);
+    stage_rows<PT>(static_cast<const PT *>(p.packed) + warp_elem0, wtile, nrows, LK, p.row_stride, lane);
+    float *trow = wtile + (lane >> p.gs_log2) * p.row_stride;
+    __syncthreads();  // level table and this warp's tile visible
+
+    const int nchunk = LK >> 2;
+    float m = -INFINITY;
+    for (int j = 0; j < nchunk; ++j) {
+        const float4 lg = *reinterpret_cast<const float4 *>(trow + 3 * LK + 4 * j);
+        m = fmaxf(m, fmaxf(fmaxf(lg.x, lg.y), fmaxf(lg.z, lg.w)));
+    }
+    float s = 0.f;
+    for (int j = 0; j < nchunk; ++j) {
+        const float4 lg = *reinterpret_cast<const float4 *>(trow + 3 * LK + 4 * j);
+        const float4 e = make_float4(__expf(lg.x - m), __expf(lg.y - m), __expf(lg.z - m), __expf(lg.w - m));
+        s += e.x + e.y + e.z + e.w;
+        if (lane_c == 0) *reinterpret_cast<float4 *>(trow + 4 * LK + 4 * j) = e;
+    }
+    const float inv = 1.0f / s;
+    __syncwarp();
+
+    const int g = row_ok ? row % p.G : 0;
+    const size_t head_elem = (size_t)b * p.N * p.GD + (size_t)g * p.D;
+    const VT *value_b = static_cast<const VT *>(p.value) + head_elem + (size_t)lane_c * CPL;
+    float *accum_b = p.accum + head_elem + (size_t)lane_c * 4;
+
+    // grad_output of this row: the lane's gather channels (for the dot products) and its
+    // scatter channels (4*lane_c + j*4*lpg, so that the lanes of a row cover contiguous bytes).
+    float go_d[CPL];
+    float go_s[NRED][4];
+    {
+        const VT *go_row = static_cast<const VT *>(p.grad_out) + ((size_t)b * p.rows_per_b + (row_ok ? row : 0)) * (size_t)p.D;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (active) raw = ldg16(go_row + (size_t)lane_c * CPL);
+        Vec16<VT>::unpack(raw, go_d);
+#pragma unroll
+        for (int r = 0; r < NRED; ++r) {
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (active) f = load4<VT>(go_row + r * 4 * p.lpg + 4 * lane_c);
+            go_s[r][0] = f.x; go_s[r][1] = f.y; go_s[r][2] = f.z; go_s[r][3] = f.w;
+        }
+    }
+    const int red_stride = 4 * p.lpg;
+
+    float S = 0.f;  // sum_i p_i * dalpha_i
+    for (int j = 0; j < nchunk; ++j) {
+        const float4 c0 = *reinterpret_cast<const float4 *>(trow + 12 * j);
+        const float4 c1 = *reinterpret_cast<const float4 *>(trow + 12 * j + 4);
+        const float4 c2 = *reinterpret_cast<const float4 *>(trow + 12 * j + 8);
+        const float4 e4 = *reinterpret_cast<const float4 *>(trow + 4 * LK + 4 * j);
+        const float xs[4] = {c0.x, c0.w, c1.z, c2.y};
+        const float ys[4] = {c0.y, c1.x, c1.w, c2.z};
+        const float zs[4] = {c0.z, c1.y, c2.x, c2.w};
+        const float es[4] = {e4.x, e4.y, e4.z, e4.w};
+        const LevelGeom lv = geom[j >> p.k_shift];
+        const VT *lvl = value_b + (size_t)lv.start * p.GD;
+        float *acc_lvl = accum_b + (size_t)lv.start * p.GD;
+        float gxs[4], gys[4], gzs[4], das[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const float a = es[t] * inv;
+            PointGeom pg;
+            point_geometry(lv, p.GD, xs[t], ys[t], zs[t], pg);
+            uint4 raw[8];
+            bool in[8];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                in[n] = active && pg.zin[n >> 2] && pg.yin[(n >> 1) & 1] && pg.xin[n & 1];
+                raw[n] = in[n] ? ldg16(lvl + pg.off[n]) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            float dot[8];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const float w = (pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2];
+                const float aw = a * w;
+                if (in[n]) {
+                    float *dst = acc_lvl + pg.off[n];
+#pragma unroll
+                    for (int r = 0; r < NRED; ++r)
+                        red_add_f32x4(dst + r * red_stride, aw * go_s[r][0], aw * go_s[r][1], aw * go_s[r][2], aw * go_s[r][3]);
+                }
+                float v[CPL];
+                Vec16<VT>::unpack(raw[n], v);
+                float d = 0.f;
+#pragma unroll
+                for (int k = 0; k < CPL; ++k) d = fmaf(v[k], go_d[k], d);
+                dot[n] = d;  // 0 for corners outside the level
+            }
+            // d out / d x_im = sum_{z,y} wz*wy*(dot[z,y,1] - dot[z,y,0]), likewise y and z; dalpha = sum w*dot
+            const float wzy[4] = {pg.wz[0] * pg.wy[0], pg.wz[0] * pg.wy[1], pg.wz[1] * pg.wy[0], pg.wz[1] * pg.wy[1]};
+            const float wzx[4] = {pg.wz[0] * pg.wx[0], pg.wz[0] * pg.wx[1], pg.wz[1] * pg.wx[0], pg.wz[1] * pg.wx[1]};
+            const float wyx[4] = {pg.wy[0] * pg.wx[0], pg.wy[0] * pg.wx[1], pg.wy[1] * pg.wx[0], pg.wy[1] * pg.wx[1]};
+            float gx = wzy[0] * (dot[1] - dot[0]) + wzy[1] * (dot[3] - dot[2]) + wzy[2] * (dot[5] - dot[4]) + wzy[3] * (dot[7] - dot[6]);
+            float gy = wzx[0] * (dot[2] - dot[0]) + wzx[1] * (dot[3] - dot[1]) + wzx[2] * (dot[6] - dot[4]) + wzx[3] * (dot[7] - dot[5]);
+            float gz = wyx[0] * (dot[4] - dot[0]) + wyx[1] * (dot[5] - dot[1]) + wyx[2] * (dot[6] - dot[2]) + wyx[3] * (dot[7] - dot[3]);
+            float da = 0.f;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) da = fmaf((pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2], dot[n], da);
+            for (int mask = gs >> 1; mask > 0; mask >>= 1) {
+                gx += __shfl_xor_sync(0xffffffffu, gx, mask);
+                gy += __shfl_xor_sync(0xffffffffu, gy, mask);
+                gz += __shfl_xor_sync(0xffffffffu, gz, mask);
+                da += __shfl_xor_sync(0xffffffffu, da, mask);
+            }
+            gxs[t] = a * (float)lv.W * gx;
+            gys[t] = a * (float)lv.H * gy;
+            gzs[t] = a * (float)lv.D * gz;
+            das[t] = da;
+            S = fmaf(a, da, S);
+        }
+        __syncwarp();  // every lane of the row has read this chunk's coordinates
+        if (lane_c == 0) {
+            *reinterpret_cast<float4 *>(trow + 12 * j) = make_float4(gxs[0], gys[0], gzs[0], gxs[1]);
+            *reinterpret_cast<float4 *>(trow + 12 * j + 4) = make_float4(gys[1], gzs[1], gxs[2], gys[2]);
+            *reinterpret_cast<float4 *>(trow + 12 * j + 8) = make_float4(gzs[2], gxs[3], gys[3], gzs[3]);
+            *reinterpret_cast<float4 *>(trow + 3 * LK + 4 * j) = make_float4(das[0], das[1], das[2], das[3]);
+        }
+    }
+    __syncwarp();
+    for (int i = lane_c; i < LK; i += gs) {
+        const float a = trow[4 * LK + i] * inv;
+        trow[3 * LK + i] = a * (trow[3 * LK + i] - S);
+    }
+    __syncwarp();
+
+    // coalesced write-back of the finished gradient rows of this warp
+    PT *dst = static_cast<PT *>(p.grad_packed) + warp_elem0;
+    const int nvec = nrows * LK;
+    for (int v = lane; v < nvec; v += 32) {
+        const int r = v / LK;
+        const int c = (v - r * LK) * 4;
+        store4<PT>(dst + (size_t)v * 4, *reinterpret_cast<const float4 *>(wtile + r * p.row_stride + c));
+    }
+}
+
+// fp32 accumulation image -> grad_value in a 16-bit dtype; n4 = number of 4-element vectors.
+template <typename VT>
+__global__ void __launch_bounds__(256) fda_cast_kernel(const float *__restrict__ accum, VT *__restrict__ out, size_t n4) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 f = __ldcs(reinterpret_cast<const float4 *>(accum) + i);
+        store4<VT>(out + i * 4, f);
+    }
+}
+
+}  // namespace fda

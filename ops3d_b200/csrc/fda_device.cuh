@@ -1,0 +1,204 @@
+// Device-side building blocks shared by the forward and backward kernels of
+// Flash Deformable 3D Attention for sm_100a.
+//
+// Thread mapping (both directions).  One "row" is one (query, head) pair of a
+// batch element; its D channels are covered by `lpg` lanes that each own one
+// 16-byte vector of the value dtype (8 channels for 16-bit types, 4 for fp32).
+// Lanes of a row form a power-of-two group of `gs = 1 << gs_log2 >= lpg` lanes
+// inside one warp (surplus lanes idle), so a warp-wide load instruction fetches
+// 32/gs complete head rows (64 B each at D = 32, bf16): every 32-byte sector that
+// crosses the memory system is fully used, which is what a random 8-corner
+// gather can at best achieve.
+//
+// Coordinates follow torch.nn.functional.grid_sample(align_corners=False,
+// padding_mode="zeros") bit for bit in fp32 -- un-normalisation
+// ((g + 1) * size - 1) / 2 on g = 2*loc - 1, weights (x0 + 1) - x and x - x0 --
+// because the parity target is the reference's PyTorch implementation
+// (ops3d/flash_deform_attn.py:139-165).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fda {
+
+constexpr int kMaxLevels = 5;
+constexpr int kThreads = 256;
+constexpr int kWarpsPerBlock = kThreads / 32;
+
+struct LevelGeom {
+    int D, H, W;
+    int start;  // first cell of the level inside one batch element
+};
+
+// Kernel parameter block (passed by value).
+struct Problem {
+    const void *value;
+    const int64_t *shapes;
+    const int64_t *lsi;
+    const void *packed;
+    void *out;              // forward only
+    const void *grad_out;   // backward only
+    float *accum;           // backward: fp32 image of grad_value
+    void *grad_packed;      // backward
+    int B, N, G, D, L, K, Q;
+    int LK;          // L * K
+    int k_shift;     // log2(K / 4): level of 4-point chunk j is j >> k_shift
+    int gs_log2;     // log2 of lanes per row group
+    int lpg;         // active lanes per row = D / channels-per-lane
+    int rows_per_b;  // Q * G
+    int GD;          // G * D
+    int row_stride;  // floats per staged row in shared memory
+};
+
+// ---------------------------------------------------------------------------
+// dtype traits: one 16-byte vector of the value dtype <-> fp32 registers
+// ---------------------------------------------------------------------------
+template <typename T> struct Vec16;
+
+template <> struct Vec16<float> {
+    static constexpr int kCPL = 4;
+    static __device__ __forceinline__ void unpack(const uint4 &r, float (&v)[4]) {
+        v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y);
+        v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&v)[4]) {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    }
+};
+
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int kCPL = 8;
+    static __device__ __forceinline__ void unpack(const uint4 &r, float (&v)[8]) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // bf16 is the high half of an fp32
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+template <> struct Vec16<__half> {
+    static constexpr int kCPL = 8;
+    static __device__ __forceinline__ void unpack(const uint4 &r, float (&v)[8]) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// Four consecutive elements (aligned to four elements) <-> float4.
+template <typename T> __device__ __forceinline__ float4 load4(const T *p);
+template <> __device__ __forceinline__ float4 load4<float>(const float *p) {
+    return __ldg(reinterpret_cast<const float4 *>(p));
+}
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2 *>(p));
+    return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
+                       __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float4 load4<__half>(const __half *p) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2 *>(p));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T> __device__ __forceinline__ void store4(T *p, const float4 &v);
+template <> __device__ __forceinline__ void store4<float>(float *p, const float4 &v) {
+    *reinterpret_cast<float4 *>(p) = v;
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16 *p, const float4 &v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(p) = make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
+}
+template <> __device__ __forceinline__ void store4<__half>(__half *p, const float4 &v) {
+    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(p) = make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
+}
+
+// 16-byte read-only gather load.
+__device__ __forceinline__ uint4 ldg16(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+
+// fp32 x4 reduction into global memory (one 16-byte L2 atomic operation, no return value).
+__device__ __forceinline__ void red_add_f32x4(float *p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Geometry of one sampling point: corner offsets, validity and weights
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float unnormalize(float loc, float size) {
+    // grid = 2*loc - 1 (done by the PyTorch oracle before grid_sample), then
+    // grid_sample's ((grid + 1) * size - 1) / 2; every step rounded on its own.
+    const float g = __fadd_rn(__fmul_rn(2.0f, loc), -1.0f);
+    return __fmul_rn(__fadd_rn(__fmul_rn(__fadd_rn(g, 1.0f), size), -1.0f), 0.5f);
+}
+
+struct PointGeom {
+    float wx[2], wy[2], wz[2];   // weight of the low / high corner along each axis
+    bool xin[2], yin[2], zin[2]; // corner index inside the level along each axis
+    uint32_t off[8];             // element offset of corner (dz,dy,dx) -> index dz*4+dy*2+dx, modulo 2^32
+};
+
+__device__ __forceinline__ void point_geometry(const LevelGeom &lv, int GD, float x, float y, float z, PointGeom &pg) {
+    const float xi = unnormalize(x, (float)lv.W);
+    const float yi = unnormalize(y, (float)lv.H);
+    const float zi = unnormalize(z, (float)lv.D);
+    const float xf = floorf(xi), yf = floorf(yi), zf = floorf(zi);
+    pg.wx[0] = __fsub_rn(__fadd_rn(xf, 1.0f), xi); pg.wx[1] = __fsub_rn(xi, xf);
+    pg.wy[0] = __fsub_rn(__fadd_rn(yf, 1.0f), yi); pg.wy[1] = __fsub_rn(yi, yf);
+    pg.wz[0] = __fsub_rn(__fadd_rn(zf, 1.0f), zi); pg.wz[1] = __fsub_rn(zi, zf);
+    // float -> int conversion saturates; the unsigned compares below reject every index outside
+    // [0, size), including saturated and wrapped ones, so no out-of-range address is ever formed.
+    const uint32_t x0 = (uint32_t)(int)xf, y0 = (uint32_t)(int)yf, z0 = (uint32_t)(int)zf;
+    const uint32_t W = (uint32_t)lv.W, H = (uint32_t)lv.H, Dz = (uint32_t)lv.D;
+    pg.xin[0] = x0 < W; pg.xin[1] = (x0 + 1u) < W;
+    pg.yin[0] = y0 < H; pg.yin[1] = (y0 + 1u) < H;
+    pg.zin[0] = z0 < Dz; pg.zin[1] = (z0 + 1u) < Dz;
+    const uint32_t sx = (uint32_t)GD, sy = W * sx, sz = H * sy;
+    const uint32_t base = z0 * sz + y0 * sy + x0 * sx;  // wraps for index -1; base + stride wraps back
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+        pg.off[n] = base + ((n & 4) ? sz : 0u) + ((n & 2) ? sy : 0u) + ((n & 1) ? sx : 0u);
+}
+
+// Stage `nrows` consecutive packed rows (4*LK elements each, contiguous in global memory) into a
+// warp-private shared-memory tile as fp32, `row_stride` floats apart.  Whole warp participates.
+template <typename PT>
+__device__ __forceinline__ void stage_rows(const PT *__restrict__ src, float *tile, int nrows, int LK, int row_stride, int lane) {
+    const int nvec = nrows * LK;  // 4-element vectors
+    for (int v = lane; v < nvec; v += 32) {
+        const int r = v / LK;
+        const int c = (v - r * LK) * 4;
+        const float4 f = load4<PT>(src + (size_t)v * 4);
+        *reinterpret_cast<float4 *>(tile + r * row_stride + c) = f;
+    }
+}
+
+}  // namespace fda

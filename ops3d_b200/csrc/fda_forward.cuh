@@ -1,0 +1,127 @@
+// Forward kernel of Flash Deformable 3D Attention for sm_100a.
+//
+// Replaces forward_kernel_reg / forward_kernel of the reference
+// (csrc/cuda/flash_deform_im2col_cuda.cuh:190-295 and :50-186) and its trilinear
+// helper (csrc/cuda/common.h:52-138) with one kernel in two staging flavours:
+//   kStage = false  every lane reads its row's logits and coordinates straight from
+//                   global memory (lanes of a row read the same addresses, which the
+//                   load unit merges); nothing is shared between threads.
+//   kStage = true   each warp first copies the packed rows it owns (contiguous in
+//                   global memory) into a private shared-memory tile with fully
+//                   coalesced vector loads, converted to fp32.
+// Per row: soft-max over the L*K logits, then for each point the 8-corner trilinear
+// gather with one predicated 16-byte load per corner and lane, fp32 accumulation, and
+// one 16-byte store of the finished channels.  No thread block barrier besides the one
+// that publishes the level table; warps never wait on each other.
+#pragma once
+
+#include "fda_device.cuh"
+
+namespace fda {
+
+template <typename VT, typename PT, bool kStage>
+__global__ void __launch_bounds__(kThreads, 2) fda_forward_kernel(const Problem p) {
+    constexpr int CPL = Vec16<VT>::kCPL;
+    __shared__ LevelGeom geom[kMaxLevels];
+    extern __shared__ __align__(16) float smem_tile[];
+
+    const int tid = threadIdx.x;
+    if (tid < p.L) {
+        LevelGeom lv;
+        lv.D = (int)p.shapes[3 * tid];
+        lv.H = (int)p.shapes[3 * tid + 1];
+        lv.W = (int)p.shapes[3 * tid + 2];
+        lv.start = (int)p.lsi[tid];
+        geom[tid] = lv;
+    }
+
+    const int b = blockIdx.y;
+    const int gs = 1 << p.gs_log2;
+    const int lane_c = tid & (gs - 1);
+    const int rows_per_block = (int)blockDim.x >> p.gs_log2;
+    const int row = blockIdx.x * rows_per_block + (tid >> p.gs_log2);  // q * G + g inside batch element b
+    const bool row_ok = row < p.rows_per_b;
+    const bool active = row_ok && lane_c < p.lpg;
+    const int LK = p.LK;
+
+    const PT *packed_row = static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + (row_ok ? row : 0)) * (size_t)(4 * LK);
+    const float *tile_row = nullptr;
+    if (kStage) {
+        const int warp = tid >> 5, lane = tid & 31;
+        const int rows_per_warp = 32 >> p.gs_log2;
+        const int first = blockIdx.x * rows_per_block + warp * rows_per_warp;
+        float *wtile = smem_tile + warp * rows_per_warp * p.row_stride;
+        int nrows = p.rows_per_b - first;
+        nrows = nrows < 0 ? 0 : (nrows > rows_per_warp ? rows_per_warp : nrows);
+        stage_rows<PT>(static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + first) * (size_t)(4 * LK),
+                       wtile, nrows, LK, p.row_stride, lane);
+        tile_row = wtile + ((tid & 31) >> p.gs_log2) * p.row_stride;
+    }
+    __syncthreads();  // level table (and, when staging, this warp's tile) visible
+
+    // Four consecutive row elements starting at element `e` (a multiple of 4), as fp32.
+    auto get4 = [&](int e) -> float4 {
+        if (!row_ok) return make_float4(0.f, 0.f, 0.f, 0.f);
+        if (kStage) return *reinterpret_cast<const float4 *>(tile_row + e);
+        return load4<PT>(packed_row + e);
+    };
+
+    // soft-max statistics over the L*K logits of this row
+    const int nchunk = LK >> 2;
+    float m = -INFINITY;
+    for (int j = 0; j < nchunk; ++j) {
+        const float4 lg = get4(3 * LK + 4 * j);
+        m = fmaxf(m, fmaxf(fmaxf(lg.x, lg.y), fmaxf(lg.z, lg.w)));
+    }
+    float s = 0.f;
+    for (int j = 0; j < nchunk; ++j) {
+        const float4 lg = get4(3 * LK + 4 * j);
+        s += __expf(lg.x - m) + __expf(lg.y - m) + __expf(lg.z - m) + __expf(lg.w - m);
+    }
+    const float inv = 1.0f / s;
+
+    const int g = row_ok ? row % p.G : 0;
+    const VT *value_b = static_cast<const VT *>(p.value) + (size_t)b * p.N * p.GD + (size_t)g * p.D + (size_t)lane_c * CPL;
+
+    float acc[CPL];
+#pragma unroll
+    for (int k = 0; k < CPL; ++k) acc[k] = 0.f;
+
+    for (int j = 0; j < nchunk; ++j) {
+        const float4 c0 = get4(12 * j), c1 = get4(12 * j + 4), c2 = get4(12 * j + 8);
+        const float4 lg = get4(3 * LK + 4 * j);
+        const float xs[4] = {c0.x, c0.w, c1.z, c2.y};
+        const float ys[4] = {c0.y, c1.x, c1.w, c2.z};
+        const float zs[4] = {c0.z, c1.y, c2.x, c2.w};
+        const float ls[4] = {lg.x, lg.y, lg.z, lg.w};
+        const LevelGeom lv = geom[j >> p.k_shift];
+        const VT *lvl = value_b + (size_t)lv.start * p.GD;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const float a = __expf(ls[t] - m) * inv;
+            PointGeom pg;
+            point_geometry(lv, p.GD, xs[t], ys[t], zs[t], pg);
+            uint4 raw[8];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const bool in = active && pg.zin[n >> 2] && pg.yin[(n >> 1) & 1] && pg.xin[n & 1];
+                raw[n] = in ? ldg16(lvl + pg.off[n]) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const float w = a * ((pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2]);
+                float v[CPL];
+                Vec16<VT>::unpack(raw[n], v);
+#pragma unroll
+                for (int k = 0; k < CPL; ++k) acc[k] = fmaf(w, v[k], acc[k]);
+            }
+        }
+    }
+
+    if (active) {
+        VT *dst = static_cast<VT *>(p.out) + ((size_t)b * p.rows_per_b + row) * (size_t)p.D + (size_t)lane_c * CPL;
+        *reinterpret_cast<uint4 *>(dst) = Vec16<VT>::pack(acc);
+    }
+}
+
+}  // namespace fda

@@ -140,11 +140,12 @@ def fused_forward_backward(value, spatial_shapes, packed, grad_out, K: int, chun
     grad_value = torch.zeros_like(value32)
     outs, gpacked = [], []
     for q0 in range(0, Q, chunk):
-        v = value32.clone().requires_grad_(True)
-        pk = packed32[:, q0:q0 + chunk].clone().requires_grad_(True)
-        loc, logits = unpack_loc_attn(pk, L, K)
-        out = ms_deform_attn_core_pytorch_3d(v, shapes, loc, _softmax_lk(logits))
-        out.backward(grad_out[:, q0:q0 + chunk].reshape_as(out))
+        with torch.enable_grad():  # also usable from inside another autograd backward
+            v = value32.clone().requires_grad_(True)
+            pk = packed32[:, q0:q0 + chunk].clone().requires_grad_(True)
+            loc, logits = unpack_loc_attn(pk, L, K)
+            out = ms_deform_attn_core_pytorch_3d(v, shapes, loc, _softmax_lk(logits))
+            out.backward(grad_out[:, q0:q0 + chunk].reshape_as(out))
         grad_value += v.grad
         gpacked.append(pk.grad)
         outs.append(out.detach())

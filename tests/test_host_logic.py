@@ -1,0 +1,61 @@
+"""Host-side mirror of the reference's Python interface (no device needed)."""
+import pytest
+import torch
+
+import ops3d_b200
+from ops3d_b200 import FlashDeformAttnFunction
+from ops3d_b200.flash_deform_attn import findspec, findspec_bwd
+
+# (B, Q, G, C) -> (findspec, findspec_bwd) as returned by the reference's own functions
+# (ops3d/flash_deform_attn.py:26-62) for these arguments.
+REFERENCE_SPECS = {
+    (1, 288, 4, 16): ((8, 384), (1, 256)),
+    (2, 4608, 8, 32): ((8, 512), (1, 256)),
+    (4, 200, 8, 32): ((8, 512), (1, 256)),
+    (1, 4096, 8, 64): ((8, 512), (2, 256)),
+    (1, 294912, 8, 48): ((8, 432), (2, 192)),
+    (5, 64, 4, 32): ((8, 512), (1, 256)),
+    (64, 64, 4, 32): ((8, 512), (1, 256)),
+    (1, 1, 4, 32): ((8, 16), (1, 128)),
+    (3, 7, 2, 8): ((8, 42), (1, 112)),
+}
+
+
+@pytest.mark.parametrize("shape,want", sorted(REFERENCE_SPECS.items()))
+def test_launch_hints_equal_the_reference(shape, want):
+    assert findspec(*shape) == want[0]
+    assert findspec_bwd(*shape) == want[1]
+
+
+def test_launch_hints_are_cheap_at_full_size():
+    import time
+    t = time.perf_counter()
+    findspec(2, 598016, 8, 32), findspec_bwd(2, 598016, 8, 32)
+    assert time.perf_counter() - t < 0.05  # the reference's divisor scan takes ~40 ms here per call
+
+
+def test_public_names():
+    assert ops3d_b200._C is not None, "torch binding not built"
+    assert hasattr(ops3d_b200._C, "flash_deform_attn_forward") and hasattr(ops3d_b200._C, "flash_deform_attn_backward")
+    assert callable(FlashDeformAttnFunction.apply)
+
+
+def _cpu_inputs(L=2, K=4, L_packed=None):
+    shapes = torch.tensor([[4, 4, 4]] * L, dtype=torch.long)
+    lsi = torch.cat((shapes.new_zeros(1), shapes.prod(1).cumsum(0)[:-1]))
+    value = torch.rand(1, int(shapes.prod(1).sum()), 4, 32)
+    Lp = L if L_packed is None else L_packed
+    packed = torch.rand(1, 16, 4, Lp * K * 4)
+    return value, shapes, lsi, packed
+
+
+def test_last_dimension_mismatch_raises_value_error():
+    value, shapes, lsi, packed = _cpu_inputs(L=2, L_packed=1)
+    with pytest.raises(ValueError, match="does not match"):
+        FlashDeformAttnFunction.apply(value, shapes, lsi, packed, 1, 4, True)
+
+
+def test_cpu_tensors_raise_instead_of_falling_back():
+    value, shapes, lsi, packed = _cpu_inputs()
+    with pytest.raises((RuntimeError, AssertionError)):
+        FlashDeformAttnFunction.apply(value, shapes, lsi, packed, 1, 4, True)
