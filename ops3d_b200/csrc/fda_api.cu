@@ -4,6 +4,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <set>
 #include <utility>
@@ -45,6 +46,30 @@ int validate(const Shape &s, int im2col_step) {
     return FDA_OK;
 }
 
+// Bytes of re-used data the kernels may mark "evict last": a fraction of the device's L2
+// (FDA_L2_KEEP_FRACTION overrides the default; 0 disables the hints' effect).
+unsigned long long l2_keep_budget() {
+    static std::mutex mu;
+    static std::map<int, int> l2_bytes;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    int l2 = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = l2_bytes.find(dev);
+        if (it == l2_bytes.end()) {
+            if (cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev) != cudaSuccess) l2 = 0;
+            l2_bytes[dev] = l2;
+        } else {
+            l2 = it->second;
+        }
+    }
+    double frac = 0.7;
+    if (const char *e = std::getenv("FDA_L2_KEEP_FRACTION")) frac = std::atof(e);
+    if (frac < 0) frac = 0;
+    return (unsigned long long)(frac * (double)l2);
+}
+
 fda::Problem make_problem(const Shape &s) {
     fda::Problem p;
     std::memset(&p, 0, sizeof(p));
@@ -57,6 +82,8 @@ fda::Problem make_problem(const Shape &s) {
     p.gs_log2 = lg;
     p.rows_per_b = s.Q * s.G;
     p.GD = s.G * s.D;
+    p.value_elem_bytes = dtype_size(s.vdt);
+    p.l2_keep_bytes = l2_keep_budget();
     return p;
 }
 

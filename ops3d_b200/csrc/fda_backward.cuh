@@ -29,14 +29,8 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
     extern __shared__ __align__(16) float smem_tile[];
 
     const int tid = threadIdx.x;
-    if (tid < p.L) {
-        LevelGeom lv;
-        lv.D = (int)p.shapes[3 * tid];
-        lv.H = (int)p.shapes[3 * tid + 1];
-        lv.W = (int)p.shapes[3 * tid + 2];
-        lv.start = (int)p.lsi[tid];
-        geom[tid] = lv;
-    }
+    if (tid == 0) build_level_table(geom, p.shapes, p.lsi, p.L, p.GD, p.value_elem_bytes, true, p.l2_keep_bytes);
+    const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
 
     const int b = blockIdx.y;
     const int gs = 1 << p.gs_log2;
@@ -88,7 +82,7 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
     {
         const VT *go_row = static_cast<const VT *>(p.grad_out) + ((size_t)b * p.rows_per_b + (row_ok ? row : 0)) * (size_t)p.D;
         uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (active) raw = ldg16(go_row + (size_t)lane_c * CPL);
+        if (active) raw = ldg16_hint(go_row + (size_t)lane_c * CPL, pol_stream);
         Vec16<VT>::unpack(raw, go_d);
 #pragma unroll
         for (int r = 0; r < NRED; ++r) {
@@ -112,6 +106,8 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
         const LevelGeom lv = geom[j >> p.k_shift];
         const VT *lvl = value_b + (size_t)lv.start * p.GD;
         float *acc_lvl = accum_b + (size_t)lv.start * p.GD;
+        const uint64_t pol_v = (lv.keep & 1) ? pol_keep : pol_stream;
+        const uint64_t pol_g = (lv.keep & 2) ? pol_keep : pol_stream;
         float gxs[4], gys[4], gzs[4], das[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -123,7 +119,7 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 in[n] = active && pg.zin[n >> 2] && pg.yin[(n >> 1) & 1] && pg.xin[n & 1];
-                raw[n] = in[n] ? ldg16(lvl + pg.off[n]) : make_uint4(0u, 0u, 0u, 0u);
+                raw[n] = in[n] ? ldg16_hint(lvl + pg.off[n], pol_v) : make_uint4(0u, 0u, 0u, 0u);
             }
             float dot[8];
 #pragma unroll
@@ -134,7 +130,7 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
                     float *dst = acc_lvl + pg.off[n];
 #pragma unroll
                     for (int r = 0; r < NRED; ++r)
-                        red_add_f32x4(dst + r * red_stride, aw * go_s[r][0], aw * go_s[r][1], aw * go_s[r][2], aw * go_s[r][3]);
+                        red_add_f32x4_hint(dst + r * red_stride, aw * go_s[r][0], aw * go_s[r][1], aw * go_s[r][2], aw * go_s[r][3], pol_g);
                 }
                 float v[CPL];
                 Vec16<VT>::unpack(raw[n], v);
@@ -186,7 +182,7 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
     for (int v = lane; v < nvec; v += 32) {
         const int r = v / LK;
         const int c = (v - r * LK) * 4;
-        store4<PT>(dst + (size_t)v * 4, *reinterpret_cast<const float4 *>(wtile + r * p.row_stride + c));
+        store4_stream<PT>(dst + (size_t)v * 4, *reinterpret_cast<const float4 *>(wtile + r * p.row_stride + c));
     }
 }
 

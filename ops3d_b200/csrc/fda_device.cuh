@@ -31,6 +31,7 @@ constexpr int kWarpsPerBlock = kThreads / 32;
 struct LevelGeom {
     int D, H, W;
     int start;  // first cell of the level inside one batch element
+    int keep;   // bit 0: keep this level's value rows in L2, bit 1: keep its fp32 gradient image in L2
 };
 
 // Kernel parameter block (passed by value).
@@ -51,6 +52,8 @@ struct Problem {
     int rows_per_b;  // Q * G
     int GD;          // G * D
     int row_stride;  // floats per staged row in shared memory
+    unsigned long long l2_keep_bytes;  // how much per-batch-element data may be marked "evict last" in L2
+    int value_elem_bytes;              // sizeof(value dtype)
 };
 
 // ---------------------------------------------------------------------------
@@ -142,12 +145,97 @@ template <> __device__ __forceinline__ void store4<__half>(__half *p, const floa
     *reinterpret_cast<uint2 *>(p) = make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
 }
 
+// Streaming (read-once / write-once, evict-first) variants for the per-query rows.
+template <typename T> __device__ __forceinline__ float4 load4_stream(const T *p);
+template <> __device__ __forceinline__ float4 load4_stream<float>(const float *p) {
+    return __ldcs(reinterpret_cast<const float4 *>(p));
+}
+template <> __device__ __forceinline__ float4 load4_stream<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    const uint2 r = __ldcs(reinterpret_cast<const uint2 *>(p));
+    return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
+                       __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float4 load4_stream<__half>(const __half *p) {
+    const uint2 r = __ldcs(reinterpret_cast<const uint2 *>(p));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void store4_stream(T *p, const float4 &v);
+template <> __device__ __forceinline__ void store4_stream<float>(float *p, const float4 &v) {
+    __stcs(reinterpret_cast<float4 *>(p), v);
+}
+template <> __device__ __forceinline__ void store4_stream<__nv_bfloat16>(__nv_bfloat16 *p, const float4 &v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    __stcs(reinterpret_cast<uint2 *>(p), make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b)));
+}
+template <> __device__ __forceinline__ void store4_stream<__half>(__half *p, const float4 &v) {
+    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    __stcs(reinterpret_cast<uint2 *>(p), make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b)));
+}
+
 // 16-byte read-only gather load.
 __device__ __forceinline__ uint4 ldg16(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
 
 // fp32 x4 reduction into global memory (one 16-byte L2 atomic operation, no return value).
 __device__ __forceinline__ void red_add_f32x4(float *p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// L2 eviction-priority policies.  The gather re-reads small pyramid levels hundreds of times while
+// the largest level and the per-query rows stream through once; marking the former "evict last"
+// and the latter "evict first" keeps the re-used levels resident in the 126 MB L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint4 ldg16_hint(const void *p, uint64_t pol) {
+    uint4 r;
+    asm("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+        : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p), "l"(pol));
+    return r;
+}
+__device__ __forceinline__ void red_add_f32x4_hint(float *p, float a, float b, float c, float d, uint64_t pol) {
+    asm volatile("red.global.add.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
+                 ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void stg16_hint(void *p, const uint4 &v, uint64_t pol) {
+    asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1, %2, %3, %4}, %5;"
+                 ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(pol) : "memory");
+}
+
+// Level table in shared memory, built by one thread.  Levels are taken smallest first; a level's
+// fp32 gradient image (backward only; a miss there costs a 128-byte read AND write-back) and then
+// its value rows are marked "keep" while they still fit in the budget.
+__device__ __forceinline__ void build_level_table(LevelGeom *geom, const int64_t *shapes, const int64_t *lsi, int L,
+                                                  int GD, int value_elem_bytes, bool with_grad_image,
+                                                  unsigned long long budget) {
+    unsigned long long cells[kMaxLevels];
+    for (int l = 0; l < L; ++l) {
+        geom[l].D = (int)shapes[3 * l];
+        geom[l].H = (int)shapes[3 * l + 1];
+        geom[l].W = (int)shapes[3 * l + 2];
+        geom[l].start = (int)lsi[l];
+        geom[l].keep = 0;
+        cells[l] = (unsigned long long)shapes[3 * l] * shapes[3 * l + 1] * shapes[3 * l + 2];
+    }
+    unsigned done = 0;
+    for (int it = 0; it < L; ++it) {
+        int best = -1;
+        for (int l = 0; l < L; ++l)
+            if (!(done >> l & 1u) && (best < 0 || cells[l] < cells[best])) best = l;
+        done |= 1u << best;
+        const unsigned long long vbytes = cells[best] * (unsigned long long)GD * value_elem_bytes;
+        const unsigned long long gbytes = cells[best] * (unsigned long long)GD * 4ull;
+        if (with_grad_image && gbytes <= budget) { geom[best].keep |= 2; budget -= gbytes; }
+        if (vbytes <= budget) { geom[best].keep |= 1; budget -= vbytes; }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -196,7 +284,7 @@ __device__ __forceinline__ void stage_rows(const PT *__restrict__ src, float *ti
     for (int v = lane; v < nvec; v += 32) {
         const int r = v / LK;
         const int c = (v - r * LK) * 4;
-        const float4 f = load4<PT>(src + (size_t)v * 4);
+        const float4 f = load4_stream<PT>(src + (size_t)v * 4);
         *reinterpret_cast<float4 *>(tile + r * row_stride + c) = f;
     }
 }

@@ -26,14 +26,8 @@ __global__ void __launch_bounds__(kThreads, 2) fda_forward_kernel(const Problem 
     extern __shared__ __align__(16) float smem_tile[];
 
     const int tid = threadIdx.x;
-    if (tid < p.L) {
-        LevelGeom lv;
-        lv.D = (int)p.shapes[3 * tid];
-        lv.H = (int)p.shapes[3 * tid + 1];
-        lv.W = (int)p.shapes[3 * tid + 2];
-        lv.start = (int)p.lsi[tid];
-        geom[tid] = lv;
-    }
+    if (tid == 0) build_level_table(geom, p.shapes, p.lsi, p.L, p.GD, p.value_elem_bytes, false, p.l2_keep_bytes);
+    const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
 
     const int b = blockIdx.y;
     const int gs = 1 << p.gs_log2;
@@ -96,6 +90,7 @@ __global__ void __launch_bounds__(kThreads, 2) fda_forward_kernel(const Problem 
         const float ls[4] = {lg.x, lg.y, lg.z, lg.w};
         const LevelGeom lv = geom[j >> p.k_shift];
         const VT *lvl = value_b + (size_t)lv.start * p.GD;
+        const uint64_t pol = (lv.keep & 1) ? pol_keep : pol_stream;
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
             const float a = __expf(ls[t] - m) * inv;
@@ -105,7 +100,7 @@ __global__ void __launch_bounds__(kThreads, 2) fda_forward_kernel(const Problem 
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 const bool in = active && pg.zin[n >> 2] && pg.yin[(n >> 1) & 1] && pg.xin[n & 1];
-                raw[n] = in ? ldg16(lvl + pg.off[n]) : make_uint4(0u, 0u, 0u, 0u);
+                raw[n] = in ? ldg16_hint(lvl + pg.off[n], pol) : make_uint4(0u, 0u, 0u, 0u);
             }
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
@@ -120,7 +115,7 @@ __global__ void __launch_bounds__(kThreads, 2) fda_forward_kernel(const Problem 
 
     if (active) {
         VT *dst = static_cast<VT *>(p.out) + ((size_t)b * p.rows_per_b + row) * (size_t)p.D + (size_t)lane_c * CPL;
-        *reinterpret_cast<uint4 *>(dst) = Vec16<VT>::pack(acc);
+        stg16_hint(dst, Vec16<VT>::pack(acc), pol_stream);
     }
 }
 
