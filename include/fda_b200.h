@@ -135,6 +135,30 @@ int fda_backward_accumulate(const void *value, const int64_t *spatial_shapes, co
 
 int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_elements, int value_dtype, void *stream);
 
+/*
+ * Backward pass that needs no workspace from the caller and allocates nothing: same inputs,
+ * outputs and results as fda_backward, but the fp32 accumulation image sits in a fixed
+ * FDA_NOALLOC_MAX_ELEMENTS-float (64 MiB) array inside the library, present on every GPU that
+ * loads it.  Meant for callers that may not allocate device memory where they run (an engine
+ * plug-in's execute hook, a process whose pool already owns the whole GPU, a loop that cannot
+ * tolerate cudaMalloc's synchronisation).  No counterpart in the reference, whose backward
+ * always allocates its fp32 buffers through torch.
+ *
+ * Returns FDA_ERR_TOO_LARGE_STATIC when a 16-bit grad_value has more than
+ * FDA_NOALLOC_MAX_ELEMENTS elements (fp32 values accumulate in place and have no limit).
+ * The first call on each device looks up the array's device address (that device must be
+ * current); make that first call before any stream capture starts.  All calls share the one
+ * array: calls that overlap on a GPU race with each other, so keep them ordered.  The array is
+ * not cleared between calls; each call zeroes the part it uses before accumulating.
+ */
+#define FDA_NOALLOC_MAX_ELEMENTS (16u * 1024u * 1024u)
+int fda_backward_noalloc(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                         const void *sampling_loc_attn, const void *grad_output,
+                         void *grad_value, void *grad_sampling_loc_attn,
+                         int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                         int num_query, int num_points, int value_dtype, int packed_dtype,
+                         int im2col_step, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

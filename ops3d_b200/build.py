@@ -54,7 +54,8 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     srcs.append(os.path.join(ROOT, "include", "fda_b200.h"))
     if not force and _newer(LIB, srcs):
         return LIB
-    _run([_nvcc(), *NVCC_FLAGS, os.path.join(CSRC, "fda_api.cu"), "-o", LIB], verbose)
+    units = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+    _run([_nvcc(), *NVCC_FLAGS, *units, "-o", LIB], verbose)
     return LIB
 
 

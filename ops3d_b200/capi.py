@@ -17,7 +17,9 @@ DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 EXPORTS = (
     "fda_status_string", "fda_last_cuda_error", "fda_version", "fda_forward",
     "fda_backward_workspace_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
+    "fda_backward_noalloc",
 )
+NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
 
 _lib = None
 
@@ -51,6 +53,8 @@ def load() -> ctypes.CDLL:
     lib.fda_backward_accumulate.restype = i
     lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
     lib.fda_cast_grad_value.restype = i
+    lib.fda_backward_noalloc.argtypes = [vp] * 7 + [i] * 10 + [vp]
+    lib.fda_backward_noalloc.restype = i
     _lib = lib
     return lib
 
@@ -130,3 +134,16 @@ def cast_grad_value(accum, grad_value):
         check(load().fda_cast_grad_value(accum.data_ptr(), grad_value.data_ptr(), accum.numel(),
                                          DTYPE_CODE[grad_value.dtype], _stream(accum)))
     return grad_value
+
+
+def backward_noalloc(value, shapes, lsi, packed, grad_out, K, grad_value, grad_packed, im2col_step=64):
+    """``fda_backward_noalloc``: the caller passes inputs and BOTH outputs; nothing is allocated here or
+    in the library (the fp32 accumulation image is a fixed array inside ``libfda_b200.so``).  Raises
+    ``FdaError`` (status 11) when ``value`` is 16-bit and has more than ``NOALLOC_MAX_ELEMENTS`` elements."""
+    B, N, G, D, L, Q = _dims(value, shapes, packed)
+    with torch.cuda.device(value.device):
+        check(load().fda_backward_noalloc(
+            value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
+            grad_value.data_ptr(), grad_packed.data_ptr(),
+            B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype], im2col_step, _stream(value)))
+    return grad_value, grad_packed
