@@ -254,7 +254,7 @@ def run_ours(args, cfg):
     import torch.distributed as dist
 
     from ops3d_b200 import FlashDeformAttnFunction, capi
-    from ops3d_b200.sharded import query_range, sharded_flash_deform_attn
+    from ops3d_b200.sharded import PeerReducer, query_range, sharded_flash_deform_attn
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -277,12 +277,22 @@ def run_ours(args, cfg):
     out = torch.empty(B, qe - qb, G * D, dtype=vdt, device=dev)
     grad_value = torch.empty_like(value)
     grad_packed = torch.empty_like(packed)
-    accum = torch.empty(value.shape, dtype=torch.float32, device=dev) if vdt != torch.float32 else grad_value
+    use_peer = world > 1 and args.reduce == "peer"
+    reducer = PeerReducer(value.shape, vdt, dev, spatial_shapes=shapes) if use_peer else None
+    reducer_passes = reducer.passes if use_peer else None
+    accum = None
+    if not use_peer:
+        accum = torch.empty(value.shape, dtype=torch.float32, device=dev) if vdt != torch.float32 else grad_value
 
     def step(ev=None):
         if ev: ev[0].record()
         capi.forward(value, shapes, lsi, packed, K, out=out)
         if ev: ev[1].record()
+        if use_peer:
+            # per batch element: scatter on this stream, fused NVLink reduce+cast overlapped on a side stream
+            reducer.backward(value, shapes, lsi, packed, grad_out, K, grad_packed=grad_packed)
+            if ev: ev[2].record(); ev[3].record()
+            return
         capi.backward_accumulate(value, shapes, lsi, packed, grad_out, K, accum, grad_packed=grad_packed)
         if ev: ev[2].record()
         if world > 1:
@@ -328,7 +338,7 @@ def run_ours(args, cfg):
         host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (out, grad_value, grad_packed)]
         h2d = sum(t.numel() * t.element_size() for t in host_in)
         d2h = sum(t.numel() * t.element_size() for t in host_out)
-        del out, grad_value, grad_packed, accum
+        del out, grad_value, grad_packed, accum, reducer
         torch.cuda.empty_cache()
 
         def e2e_step():
@@ -391,12 +401,15 @@ def run_ours(args, cfg):
             "dtype": "bf16 value / f32 offsets, f32 accumulate" if cfg["vdt"] == "bfloat16" else "f32",
             "data": "synthetic",
             "config": {"workload": cfg["name"], "B": B, "Lq": Q, "N": N, "G": G, "D": D, "K": K, "levels": cfg["shapes"],
-                       "sharding": f"queries/{world}, value replicated, grad_value fp32 all-reduce" if world > 1 else "none",
+                       "sharding": (f"queries/{world}, value replicated, grad_value fp32 images summed by "
+                                    + ("a fused peer-memory reduce+cast kernel overlapped per batch element" if use_peer
+                                       else "NCCL all-reduce, then cast")) if world > 1 else "none",
                        "l2": "inputs larger than L2 (no flush needed)" if bm["fwd_bwd"] > 4e8 else "inputs smaller than L2"},
             "roofline": roofline,
             "e2e": {"value": (B / (e2e_ms * 1e-3)) if e2e_ms else None, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "gpu_launches": args.steps * (3 if vdt != torch.float32 else 2),
+            "gpu_launches": args.steps * ((1 + 2 * B * (len(reducer_passes) if reducer_passes else 1)) if use_peer
+                                          else (3 if vdt != torch.float32 else 2)),
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -415,6 +428,8 @@ def main():
     ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reduce", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the fp32 grad_value images are summed (fused peer-memory kernel, or NCCL all-reduce + cast)")
     ap.add_argument("--batch", type=int, default=0, help="override B (smaller case for profiler captures)")
     ap.add_argument("--queries", type=int, default=0, help="override Lq (smaller case for profiler captures)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")

@@ -136,6 +136,53 @@ int fda_backward_accumulate(const void *value, const int64_t *spatial_shapes, co
 int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_elements, int value_dtype, void *stream);
 
 /*
+ * fda_backward_accumulate restricted to the pyramid levels [level_begin, level_end), so that a
+ * multi-GPU caller can finish (and start exchanging) the largest level's part of the image while
+ * the other levels are still computed.  Launches over disjoint level ranges that together cover
+ * all levels, issued in stream order over the same buffers, give the result of one full call:
+ *   first launch   flags = FDA_BWD_ZERO_IMAGE                    (zero-fill the whole image first)
+ *   middle launch  flags = FDA_BWD_RESUME
+ *   last launch    flags = FDA_BWD_RESUME | FDA_BWD_FINALIZE
+ * (a single launch over all levels uses FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE).  Between launches
+ * grad_sampling_loc_attn holds intermediate values; it is final after the FINALIZE launch.
+ * No counterpart in the reference.
+ */
+#define FDA_BWD_ZERO_IMAGE 1
+#define FDA_BWD_RESUME 2
+#define FDA_BWD_FINALIZE 4
+int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                                   const void *sampling_loc_attn, const void *grad_output,
+                                   float *accum, void *grad_sampling_loc_attn,
+                                   int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                                   int num_query, int num_points, int value_dtype, int packed_dtype,
+                                   int im2col_step, int level_begin, int level_end, int flags, void *stream);
+
+/*
+ * Cross-GPU sum + cast of the fp32 images over peer (NVLink) memory, for the query-sharded
+ * backward: this rank sums slice `rank` (of `world` equal slices) of all ranks' images in fp32,
+ * converts it to value_dtype and stores it into every rank's grad_value.  peer_images and
+ * peer_outputs are HOST arrays of `world` DEVICE pointers, indexed by rank, that this GPU can
+ * address (peer-mapped / symmetric memory); the local rank's own buffers are entry `rank`.
+ * num_elements must be a multiple of 8.  The kernel only issues plain loads and stores and does
+ * not wait on other ranks: the caller must place a cross-rank barrier on `stream` before the call
+ * (all images complete) and after it (all pushes landed).  After the second barrier every rank's
+ * grad_value holds the identical, fully reduced result.  world <= 16.
+ * No counterpart in the reference (it has no multi-device path).
+ */
+int fda_peer_reduce_cast(const float *const *peer_images, void *const *peer_outputs, int world, int rank,
+                         size_t num_elements, int value_dtype, void *stream);
+
+/*
+ * Same exchange through NVSwitch multicast (NVLS): mc_image and mc_output are the MULTICAST
+ * addresses of the fp32 image and of grad_value (both bound on all `world` ranks).  This rank's
+ * slice is summed in the switch (multimem.ld_reduce .add.f32), converted once, and written to
+ * every rank's grad_value with multimem.st.  Same barrier contract as fda_peer_reduce_cast.
+ * No counterpart in the reference.
+ */
+int fda_multimem_reduce_cast(const float *mc_image, void *mc_output, int world, int rank,
+                             size_t num_elements, int value_dtype, void *stream);
+
+/*
  * Backward pass that needs no workspace from the caller and allocates nothing: same inputs,
  * outputs and results as fda_backward, but the fp32 accumulation image sits in a fixed
  * FDA_NOALLOC_MAX_ELEMENTS-float (64 MiB) array inside the library, present on every GPU that

@@ -17,8 +17,9 @@ DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 EXPORTS = (
     "fda_status_string", "fda_last_cuda_error", "fda_version", "fda_forward",
     "fda_backward_workspace_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
-    "fda_backward_noalloc",
+    "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
 )
+BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE = 1, 2, 4
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
 
 _lib = None
@@ -51,10 +52,16 @@ def load() -> ctypes.CDLL:
     lib.fda_backward.restype = i
     lib.fda_backward_accumulate.argtypes = [vp] * 7 + [i] * 10 + [vp]
     lib.fda_backward_accumulate.restype = i
+    lib.fda_backward_accumulate_levels.argtypes = [vp] * 7 + [i] * 13 + [vp]
+    lib.fda_backward_accumulate_levels.restype = i
     lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
     lib.fda_cast_grad_value.restype = i
     lib.fda_backward_noalloc.argtypes = [vp] * 7 + [i] * 10 + [vp]
     lib.fda_backward_noalloc.restype = i
+    lib.fda_peer_reduce_cast.argtypes = [vp, vp, i, i, sz, i, vp]
+    lib.fda_peer_reduce_cast.restype = i
+    lib.fda_multimem_reduce_cast.argtypes = [vp, vp, i, i, sz, i, vp]
+    lib.fda_multimem_reduce_cast.restype = i
     _lib = lib
     return lib
 
@@ -129,6 +136,19 @@ def backward_accumulate(value, shapes, lsi, packed, grad_out, K, accum, grad_pac
     return grad_packed
 
 
+def backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, grad_packed, level_begin, level_end,
+                               flags, im2col_step=64):
+    """``fda_backward_accumulate_levels``: one launch over the levels ``[level_begin, level_end)``."""
+    B, N, G, D, L, Q = _dims(value, shapes, packed)
+    with torch.cuda.device(value.device):
+        check(load().fda_backward_accumulate_levels(
+            value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
+            accum.data_ptr(), grad_packed.data_ptr(),
+            B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype], im2col_step,
+            level_begin, level_end, flags, _stream(value)))
+    return grad_packed
+
+
 def cast_grad_value(accum, grad_value):
     with torch.cuda.device(accum.device):
         check(load().fda_cast_grad_value(accum.data_ptr(), grad_value.data_ptr(), accum.numel(),
@@ -147,3 +167,23 @@ def backward_noalloc(value, shapes, lsi, packed, grad_out, K, grad_value, grad_p
             grad_value.data_ptr(), grad_packed.data_ptr(),
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype], im2col_step, _stream(value)))
     return grad_value, grad_packed
+
+
+def peer_reduce_cast(image_ptrs, output_ptrs, rank, num_elements, dtype, device, byte_offsets=(0, 0)):
+    """``fda_peer_reduce_cast`` on lists of per-rank device addresses (ints), e.g. the ``buffer_ptrs``
+    of two symmetric-memory allocations.  ``byte_offsets`` = (image, output) offsets added to every
+    address (to address one batch element of a larger buffer).  Runs on the current stream of
+    ``device``; the caller provides the barriers before and after."""
+    world = len(image_ptrs)
+    imgs = (ctypes.c_void_p * world)(*[p + byte_offsets[0] for p in image_ptrs])
+    outs = (ctypes.c_void_p * world)(*[p + byte_offsets[1] for p in output_ptrs])
+    with torch.cuda.device(device):
+        check(load().fda_peer_reduce_cast(imgs, outs, world, rank, num_elements, DTYPE_CODE[dtype],
+                                          torch.cuda.current_stream(device).cuda_stream))
+
+
+def multimem_reduce_cast(mc_image_ptr, mc_output_ptr, world, rank, num_elements, dtype, device, byte_offsets=(0, 0)):
+    """``fda_multimem_reduce_cast`` on the multicast addresses of two symmetric-memory allocations."""
+    with torch.cuda.device(device):
+        check(load().fda_multimem_reduce_cast(mc_image_ptr + byte_offsets[0], mc_output_ptr + byte_offsets[1], world, rank,
+                                              num_elements, DTYPE_CODE[dtype], torch.cuda.current_stream(device).cuda_stream))

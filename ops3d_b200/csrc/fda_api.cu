@@ -224,27 +224,47 @@ size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int
     return (size_t)batch * num_value * num_heads * head_dim * sizeof(float);
 }
 
+int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                                   const void *sampling_loc_attn, const void *grad_output,
+                                   float *accum, void *grad_sampling_loc_attn,
+                                   int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                                   int num_query, int num_points, int value_dtype, int packed_dtype,
+                                   int im2col_step, int level_begin, int level_end, int flags, void *stream) {
+    if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !grad_output || !accum || !grad_sampling_loc_attn)
+        return FDA_ERR_NULL_POINTER;
+    const Shape s{batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, packed_dtype};
+    if (int rc = validate(s, im2col_step)) return rc;
+    if (level_begin < 0 || level_end > num_levels || level_begin >= level_end) return FDA_ERR_BAD_LEVELS;
+    if (!aligned16(value) || !aligned16(sampling_loc_attn) || !aligned16(grad_output) || !aligned16(accum) ||
+        !aligned16(grad_sampling_loc_attn))
+        return FDA_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (flags & FDA_BWD_ZERO_IMAGE) {
+        const size_t n = (size_t)batch * num_value * num_heads * head_dim;
+        cudaError_t e = cudaMemsetAsync(accum, 0, n * sizeof(float), st);
+        if (e != cudaSuccess) return cuda_fail(e);
+    }
+    fda::Problem p = make_problem(s);
+    p.value = value; p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn;
+    p.grad_out = grad_output; p.accum = accum; p.grad_packed = grad_sampling_loc_attn;
+    const int chunks_per_level = num_points / 4;
+    p.chunk_begin = level_begin * chunks_per_level;
+    p.chunk_end = level_end * chunks_per_level;
+    p.resume = (flags & FDA_BWD_RESUME) ? 1 : 0;
+    p.finalize = (flags & FDA_BWD_FINALIZE) ? 1 : 0;
+    return FDA_DISPATCH(value_dtype, packed_dtype, (launch_backward<VT, PT>(p, st)));
+}
+
 int fda_backward_accumulate(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
                             const void *sampling_loc_attn, const void *grad_output,
                             float *accum, void *grad_sampling_loc_attn,
                             int batch, int num_value, int num_heads, int head_dim, int num_levels,
                             int num_query, int num_points, int value_dtype, int packed_dtype,
                             int im2col_step, void *stream) {
-    if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !grad_output || !accum || !grad_sampling_loc_attn)
-        return FDA_ERR_NULL_POINTER;
-    const Shape s{batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, packed_dtype};
-    if (int rc = validate(s, im2col_step)) return rc;
-    if (!aligned16(value) || !aligned16(sampling_loc_attn) || !aligned16(grad_output) || !aligned16(accum) ||
-        !aligned16(grad_sampling_loc_attn))
-        return FDA_ERR_MISALIGNED;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t n = (size_t)batch * num_value * num_heads * head_dim;
-    cudaError_t e = cudaMemsetAsync(accum, 0, n * sizeof(float), st);
-    if (e != cudaSuccess) return cuda_fail(e);
-    fda::Problem p = make_problem(s);
-    p.value = value; p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn;
-    p.grad_out = grad_output; p.accum = accum; p.grad_packed = grad_sampling_loc_attn;
-    return FDA_DISPATCH(value_dtype, packed_dtype, (launch_backward<VT, PT>(p, st)));
+    return fda_backward_accumulate_levels(value, spatial_shapes, level_start_index, sampling_loc_attn, grad_output, accum,
+                                          grad_sampling_loc_attn, batch, num_value, num_heads, head_dim, num_levels,
+                                          num_query, num_points, value_dtype, packed_dtype, im2col_step, 0,
+                                          num_levels > 0 ? num_levels : 1, FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE, stream);
 }
 
 int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_elements, int value_dtype, void *stream) {

@@ -15,6 +15,13 @@
 //     warp instruction covers whole 32-byte sectors of the accumulation image;
 //   * soft-max backward in closed form, grad_logit_i = p_i * (dalpha_i - sum_j p_j dalpha_j),
 //     instead of the reference's O((L*K)^2) Jacobian loop (:413-427).
+//
+// A launch may cover only a range of pyramid levels (4-point chunks [chunk_begin, chunk_end) of
+// every row).  A non-final launch leaves the raw dalpha of its points in the logit slots of
+// grad_packed; the final launch (`resume`) picks up the finished slots of the other chunks from
+// grad_packed, adds its own and applies the soft-max backward over all points.  This lets a
+// multi-GPU caller finish the largest level first and exchange its part of the gradient image
+// while the remaining levels are still being computed.
 #pragma once
 
 #include "fda_device.cuh"
@@ -69,6 +76,19 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
     }
     const float inv = 1.0f / s;
     __syncwarp();
+    if (p.resume) {
+        // slots of chunks handled by an earlier launch: finished coordinate gradients and raw dalpha
+        const PT *prev = static_cast<const PT *>(p.grad_packed) + warp_elem0;
+        const int nvec = nrows * LK;
+        for (int v = lane; v < nvec; v += 32) {
+            const int r = v / LK;
+            const int c = (v - r * LK) * 4;
+            const int j = c < 3 * LK ? c / 12 : (c - 3 * LK) >> 2;
+            if (j < p.chunk_begin || j >= p.chunk_end)
+                *reinterpret_cast<float4 *>(wtile + r * p.row_stride + c) = load4_stream<PT>(prev + (size_t)v * 4);
+        }
+        __syncwarp();
+    }
 
     const int g = row_ok ? row % p.G : 0;
     const size_t head_elem = (size_t)b * p.N * p.GD + (size_t)g * p.D;
@@ -93,8 +113,7 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
     }
     const int red_stride = 4 * p.lpg;
 
-    float S = 0.f;  // sum_i p_i * dalpha_i
-    for (int j = 0; j < nchunk; ++j) {
+    for (int j = p.chunk_begin; j < p.chunk_end; ++j) {
         const float4 c0 = *reinterpret_cast<const float4 *>(trow + 12 * j);
         const float4 c1 = *reinterpret_cast<const float4 *>(trow + 12 * j + 4);
         const float4 c2 = *reinterpret_cast<const float4 *>(trow + 12 * j + 8);
@@ -159,7 +178,6 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
             gys[t] = a * (float)lv.H * gy;
             gzs[t] = a * (float)lv.D * gz;
             das[t] = da;
-            S = fmaf(a, da, S);
         }
         __syncwarp();  // every lane of the row has read this chunk's coordinates
         if (lane_c == 0) {
@@ -170,11 +188,16 @@ __global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem
         }
     }
     __syncwarp();
-    for (int i = lane_c; i < LK; i += gs) {
-        const float a = trow[4 * LK + i] * inv;
-        trow[3 * LK + i] = a * (trow[3 * LK + i] - S);
+    if (p.finalize) {
+        float S = 0.f;  // sum_i p_i * dalpha_i over ALL points of the row
+        for (int i = 0; i < LK; ++i) S = fmaf(trow[4 * LK + i] * inv, trow[3 * LK + i], S);
+        __syncwarp();
+        for (int i = lane_c; i < LK; i += gs) {
+            const float a = trow[4 * LK + i] * inv;
+            trow[3 * LK + i] = a * (trow[3 * LK + i] - S);
+        }
+        __syncwarp();
     }
-    __syncwarp();
 
     // coalesced write-back of the finished gradient rows of this warp
     PT *dst = static_cast<PT *>(p.grad_packed) + warp_elem0;

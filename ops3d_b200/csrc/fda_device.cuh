@@ -54,6 +54,10 @@ struct Problem {
     int row_stride;  // floats per staged row in shared memory
     unsigned long long l2_keep_bytes;  // how much per-batch-element data may be marked "evict last" in L2
     int value_elem_bytes;              // sizeof(value dtype)
+    // backward only: the 4-point chunks [chunk_begin, chunk_end) of every row are processed by this launch
+    int chunk_begin, chunk_end;
+    int resume;    // slots of the other chunks are taken from grad_packed (written by an earlier launch)
+    int finalize;  // apply the soft-max backward to the logit slots (last launch over these rows)
 };
 
 // ---------------------------------------------------------------------------

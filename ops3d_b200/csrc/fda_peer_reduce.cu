@@ -1,0 +1,252 @@
+// Cross-GPU sum + cast of the fp32 grad_value images over NVLink peer memory (two-shot all-reduce
+// fused with the cast): rank r pulls slice r of every rank's image with plain peer loads, sums in
+// fp32 in a fixed order, converts once to the value dtype
+// and pushes the finished slice into every rank's grad_value with plain peer stores.
+//
+// Per rank 4*(R-1)/R bytes per element come in and sizeof(value)*(R-1)/R go out, against
+// 2*4*(R-1)/R each way for an fp32 ring all-reduce followed by a separate cast pass.
+//
+// The kernel contains no waits.  The caller orders it between two cross-rank barriers: every
+// rank's image complete before the first pull, every push landed before grad_value is read.
+// Only plain ld/st touch peer memory -- no multicast, no TMA.
+#include "../../include/fda_b200.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+
+namespace {
+
+constexpr int kMaxPeers = 16;
+
+struct PeerPtrs {
+    const float *img[kMaxPeers];  // position p = rank (first + p) % world, the local rank first
+    void *out[kMaxPeers];
+};
+
+template <typename VT> struct Out8;
+template <> struct Out8<float> {
+    static __device__ __forceinline__ void store(void *base, size_t unit, const float (&a)[8]) {
+        float4 *p = reinterpret_cast<float4 *>(static_cast<float *>(base) + unit * 8);
+        p[0] = make_float4(a[0], a[1], a[2], a[3]);
+        p[1] = make_float4(a[4], a[5], a[6], a[7]);
+    }
+};
+template <> struct Out8<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(void *base, size_t unit, const float (&a)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(base) + unit * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+template <> struct Out8<__half> {
+    static __device__ __forceinline__ void store(void *base, size_t unit, const float (&a)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __floats2half2_rn(a[2 * i], a[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(static_cast<__half *>(base) + unit * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// Each thread handles UNROLL 8-element units per iteration, units a whole grid-stride apart, and
+// issues all of its peer loads (2 x 16 bytes per unit and rank) before the first use, so that few
+// resident threads keep enough bytes in flight to cover NVLink latency while most SMs stay free
+// for the scatter kernel running beside it.
+template <typename VT, int WORLD, int UNROLL>
+__global__ void __launch_bounds__(512) fda_peer_reduce_cast_kernel(const PeerPtrs pp, const int world_rt,
+                                                                   size_t unit_begin, size_t unit_end) {
+    constexpr int W = WORLD > 0 ? WORLD : kMaxPeers;
+    const int world = WORLD > 0 ? WORLD : world_rt;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t u0 = unit_begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x; u0 < unit_end; u0 += stride * UNROLL) {
+        float4 lo[UNROLL][W], hi[UNROLL][W];
+#pragma unroll
+        for (int j = 0; j < UNROLL; ++j) {
+            const size_t u = u0 + (size_t)j * stride;
+#pragma unroll
+            for (int p = 0; p < W; ++p) {
+                if (p < world && u < unit_end) {
+                    const float4 *src = reinterpret_cast<const float4 *>(pp.img[p] + u * 8);
+                    lo[j][p] = __ldcg(src);      // L2 only: peer data must not be served from a stale L1 line
+                    hi[j][p] = __ldcg(src + 1);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < UNROLL; ++j) {
+            const size_t u = u0 + (size_t)j * stride;
+            if (u < unit_end) {
+                // Fixed summation order (local image first, then the ring); each element is summed by
+                // exactly one rank and broadcast, so all ranks end up with identical bits.
+                float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int p = 0; p < W; ++p) {
+                    if (p < world) {
+                        a[0] += lo[j][p].x; a[1] += lo[j][p].y; a[2] += lo[j][p].z; a[3] += lo[j][p].w;
+                        a[4] += hi[j][p].x; a[5] += hi[j][p].y; a[6] += hi[j][p].z; a[7] += hi[j][p].w;
+                    }
+                }
+#pragma unroll
+                for (int p = 0; p < W; ++p)
+                    if (p < world) Out8<VT>::store(pp.out[p], u, a);
+            }
+        }
+    }
+}
+
+// NVSwitch variant: the image and grad_value are bound to multicast objects.  One
+// multimem.ld_reduce returns the fp32 sum over all ranks of 16 bytes (the switch reads every GPU's
+// copy and adds in flight), one multimem.st writes the converted result into every GPU's copy.
+// Per rank only 1/R of the image comes in and 1/R of grad_value goes out.
+__device__ __forceinline__ float4 multimem_ld_reduce_add_f32x4(const float *mc) {
+    float4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(mc) : "memory");
+    return r;
+}
+__device__ __forceinline__ void multimem_st_16B(void *mc, const uint4 &v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                 "f"(__uint_as_float(v.w)) : "memory");
+}
+
+template <typename VT> struct Pack8;  // 8 fp32 -> the bytes of 8 elements of VT
+template <> struct Pack8<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(void *mc_base, size_t unit, const float4 &l, const float4 &h) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(l.x, l.y), b = __floats2bfloat162_rn(l.z, l.w);
+        __nv_bfloat162 c = __floats2bfloat162_rn(h.x, h.y), d = __floats2bfloat162_rn(h.z, h.w);
+        multimem_st_16B(static_cast<__nv_bfloat16 *>(mc_base) + unit * 8,
+                        make_uint4(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b),
+                                   *reinterpret_cast<uint32_t *>(&c), *reinterpret_cast<uint32_t *>(&d)));
+    }
+};
+template <> struct Pack8<__half> {
+    static __device__ __forceinline__ void store(void *mc_base, size_t unit, const float4 &l, const float4 &h) {
+        __half2 a = __floats2half2_rn(l.x, l.y), b = __floats2half2_rn(l.z, l.w);
+        __half2 c = __floats2half2_rn(h.x, h.y), d = __floats2half2_rn(h.z, h.w);
+        multimem_st_16B(static_cast<__half *>(mc_base) + unit * 8,
+                        make_uint4(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b),
+                                   *reinterpret_cast<uint32_t *>(&c), *reinterpret_cast<uint32_t *>(&d)));
+    }
+};
+template <> struct Pack8<float> {
+    static __device__ __forceinline__ void store(void *mc_base, size_t unit, const float4 &l, const float4 &h) {
+        float *p = static_cast<float *>(mc_base) + unit * 8;
+        multimem_st_16B(p, make_uint4(__float_as_uint(l.x), __float_as_uint(l.y), __float_as_uint(l.z), __float_as_uint(l.w)));
+        multimem_st_16B(p + 4, make_uint4(__float_as_uint(h.x), __float_as_uint(h.y), __float_as_uint(h.z), __float_as_uint(h.w)));
+    }
+};
+
+template <typename VT, int UNROLL>
+__global__ void __launch_bounds__(512) fda_multimem_reduce_cast_kernel(const float *mc_image, void *mc_out,
+                                                                       size_t unit_begin, size_t unit_end) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t u0 = unit_begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x; u0 < unit_end; u0 += stride * UNROLL) {
+        float4 lo[UNROLL], hi[UNROLL];
+#pragma unroll
+        for (int j = 0; j < UNROLL; ++j) {
+            const size_t u = u0 + (size_t)j * stride;
+            if (u < unit_end) {
+                lo[j] = multimem_ld_reduce_add_f32x4(mc_image + u * 8);
+                hi[j] = multimem_ld_reduce_add_f32x4(mc_image + u * 8 + 4);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < UNROLL; ++j) {
+            const size_t u = u0 + (size_t)j * stride;
+            if (u < unit_end) Pack8<VT>::store(mc_out, u, lo[j], hi[j]);
+        }
+    }
+}
+
+int env_int(const char *name, int dflt) {
+    const char *e = std::getenv(name);
+    return e ? std::atoi(e) : dflt;
+}
+
+template <typename VT>
+cudaError_t launch(const PeerPtrs &pp, int world, size_t ub, size_t ue, cudaStream_t st) {
+    const size_t units = ue - ub;
+    if (units == 0) return cudaSuccess;
+    // Few, fat blocks: the kernel is bound by NVLink, not by SM throughput (FDA_PEER_REDUCE_BLOCKS overrides).
+    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 64);
+    if (max_blocks < 1) max_blocks = 1;
+    const int threads = 512;
+    size_t blocks = (units + threads - 1) / threads;
+    if (blocks > (size_t)max_blocks) blocks = (size_t)max_blocks;
+    const unsigned g = (unsigned)blocks;
+    switch (world) {
+        case 2: fda_peer_reduce_cast_kernel<VT, 2, 4><<<g, threads, 0, st>>>(pp, world, ub, ue); break;
+        case 4: fda_peer_reduce_cast_kernel<VT, 4, 2><<<g, threads, 0, st>>>(pp, world, ub, ue); break;
+        case 8: fda_peer_reduce_cast_kernel<VT, 8, 1><<<g, threads, 0, st>>>(pp, world, ub, ue); break;
+        default: fda_peer_reduce_cast_kernel<VT, 0, 1><<<g, threads, 0, st>>>(pp, world, ub, ue); break;
+    }
+    return cudaGetLastError();
+}
+
+template <typename VT>
+cudaError_t launch_multimem(const float *mc_image, void *mc_out, size_t ub, size_t ue, cudaStream_t st) {
+    const size_t units = ue - ub;
+    if (units == 0) return cudaSuccess;
+    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 64);
+    if (max_blocks < 1) max_blocks = 1;
+    const int threads = 512;
+    size_t blocks = (units + threads - 1) / threads;
+    if (blocks > (size_t)max_blocks) blocks = (size_t)max_blocks;
+    fda_multimem_reduce_cast_kernel<VT, 4><<<(unsigned)blocks, threads, 0, st>>>(mc_image, mc_out, ub, ue);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" int fda_multimem_reduce_cast(const float *mc_image, void *mc_output, int world, int rank,
+                                        size_t num_elements, int value_dtype, void *stream) {
+    if (!mc_image || !mc_output) return FDA_ERR_NULL_POINTER;
+    if (world < 1 || rank < 0 || rank >= world) return FDA_ERR_BAD_SHAPE;
+    if (value_dtype < 0 || value_dtype > 2) return FDA_ERR_BAD_DTYPE;
+    if (num_elements % 8 != 0) return FDA_ERR_BAD_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(mc_image) & 15u) || (reinterpret_cast<uintptr_t>(mc_output) & 15u)) return FDA_ERR_MISALIGNED;
+    const size_t units = num_elements / 8;
+    const size_t ub = units * (size_t)rank / world, ue = units * (size_t)(rank + 1) / world;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (value_dtype == FDA_DTYPE_F32) e = launch_multimem<float>(mc_image, mc_output, ub, ue, st);
+    else if (value_dtype == FDA_DTYPE_F16) e = launch_multimem<__half>(mc_image, mc_output, ub, ue, st);
+    else e = launch_multimem<__nv_bfloat16>(mc_image, mc_output, ub, ue, st);
+    return e == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
+}
+
+extern "C" int fda_peer_reduce_cast(const float *const *peer_images, void *const *peer_outputs, int world, int rank,
+                                    size_t num_elements, int value_dtype, void *stream) {
+    if (!peer_images || !peer_outputs) return FDA_ERR_NULL_POINTER;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return FDA_ERR_BAD_SHAPE;
+    if (value_dtype < 0 || value_dtype > 2) return FDA_ERR_BAD_DTYPE;
+    if (num_elements % 8 != 0) return FDA_ERR_BAD_SHAPE;
+    PeerPtrs pp;
+    for (int p = 0; p < kMaxPeers; ++p) { pp.img[p] = nullptr; pp.out[p] = nullptr; }
+    for (int p = 0; p < world; ++p) {
+        const int r = (rank + p) % world;  // start with the local copy, then walk the ring
+        if (!peer_images[r] || !peer_outputs[r]) return FDA_ERR_NULL_POINTER;
+        if ((reinterpret_cast<uintptr_t>(peer_images[r]) & 15u) || (reinterpret_cast<uintptr_t>(peer_outputs[r]) & 15u))
+            return FDA_ERR_MISALIGNED;
+        pp.img[p] = peer_images[r];
+        pp.out[p] = peer_outputs[r];
+    }
+    const size_t units = num_elements / 8;
+    const size_t ub = units * (size_t)rank / world, ue = units * (size_t)(rank + 1) / world;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (value_dtype == FDA_DTYPE_F32) e = launch<float>(pp, world, ub, ue, st);
+    else if (value_dtype == FDA_DTYPE_F16) e = launch<__half>(pp, world, ub, ue, st);
+    else e = launch<__nv_bfloat16>(pp, world, ub, ue, st);
+    return e == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
+}

@@ -5,6 +5,9 @@ queries of each batch element are split into contiguous, equal ranges, ``value``
 and the forward needs no communication.  The backward has one exchange step: every rank scatters
 into its own fp32 image of ``grad_value``; the images are summed with one all-reduce (NCCL over
 NVLink on GPUs) and then cast once to the value dtype.  ``grad_sampling_loc_attn`` is row-local.
+On GPUs the default is ``PeerReducer``: the sum and the cast are one kernel over NVLink peer memory,
+overlapped per batch element with the scatter kernel of the next one (``FDA_SHARDED_REDUCE=nccl``
+selects the plain all-reduce + cast instead).
 
 The reference has no multi-device path; this wrapper is the "queries sharded, value replicated,
 grad_value all-reduced" arrangement of its single-device operator.
@@ -35,8 +38,141 @@ def shard_queries(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return t[:, b:e].contiguous()
 
 
+class PeerReducer:
+    """Backward of one rank with the cross-GPU reduction fused into the cast and overlapped with compute.
+
+    Holds two symmetric-memory buffers (every rank can address every rank's copy over NVLink): the
+    fp32 image of ``grad_value`` and the reduced ``grad_value`` itself.  Per batch element the scatter
+    kernel runs on the caller's stream; as soon as it is done a high-priority side stream runs
+    barrier -> reduce+cast kernel (``fda_multimem_reduce_cast``: my slice summed inside NVSwitch and
+    multicast back, when the buffers have a multicast binding; else ``fda_peer_reduce_cast``: pull my
+    slice from all ranks, sum, cast, push to all ranks) -> barrier, while the caller's stream already scatters the next batch element.  Only the last
+    batch element's exchange is exposed.  When ``spatial_shapes`` is given, each batch element is
+    further split into two launches -- the largest pyramid level first, the others second -- so that
+    the largest level's share of the image (most of the bytes) travels while the second launch runs.
+
+    ``backward`` returns a ``grad_value`` that aliases the symmetric buffer: it is valid until the
+    next ``backward`` call on this object (clone it to keep it longer).
+    """
+
+    def __init__(self, value_shape, dtype, device, group=None, spatial_shapes=None):
+        import os
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.shape, self.dtype, self.device = tuple(value_shape), dtype, device
+        self.image = symm_mem.empty(*self.shape, dtype=torch.float32, device=device)
+        self.out = symm_mem.empty(*self.shape, dtype=dtype, device=device)
+        self.h_image = symm_mem.rendezvous(self.image, self.group)
+        self.h_out = symm_mem.rendezvous(self.out, self.group)
+        self.image_ptrs = [int(p) for p in self.h_image.buffer_ptrs]
+        self.out_ptrs = [int(p) for p in self.h_out.buffer_ptrs]
+        self.mc_image = int(getattr(self.h_image, "multicast_ptr", 0) or 0)
+        self.mc_out = int(getattr(self.h_out, "multicast_ptr", 0) or 0)
+        mode = os.environ.get("FDA_PEER_REDUCE_MODE", "auto")  # auto | multimem | p2p
+        # measured on B200 / NVSwitch: in-switch reduction wins from 4 ranks up, plain peer loads at 2
+        want_mc = mode == "multimem" or (mode == "auto" and self.world >= 4)
+        self.use_multimem = want_mc and self.mc_image != 0 and self.mc_out != 0 and self.world > 1
+        if mode == "multimem" and not self.use_multimem:
+            raise RuntimeError("FDA_PEER_REDUCE_MODE=multimem but the buffers have no multicast binding")
+        self.side = torch.cuda.Stream(device=device, priority=-1)
+        self.per_batch = int(self.image[0].numel())
+        if self.per_batch % 8:
+            raise ValueError("elements per batch element must be a multiple of 8")
+        # Level schedule: the largest level first (when it sits at either end of the pyramid), so that
+        # its share of the image -- most of the bytes -- is exchanged while the other levels compute.
+        self.passes = None
+        if spatial_shapes is not None and os.environ.get("FDA_LEVEL_SPLIT", "1") != "0":
+            cells = [int(c) for c in torch.as_tensor(spatial_shapes).cpu().prod(1).tolist()]
+            L = len(cells)
+            gd = self.shape[2] * self.shape[3]
+            if L > 1 and sum(cells) == self.shape[1]:
+                big = max(range(L), key=lambda l: cells[l])
+                if big == 0:
+                    self.passes = [(0, 1), (1, L)]
+                elif big == L - 1:
+                    self.passes = [(L - 1, L), (0, L - 1)]
+                if self.passes:
+                    starts = [sum(cells[:l]) for l in range(L + 1)]
+                    self.ranges = [(starts[a] * gd, starts[b] * gd) for a, b in self.passes]  # element ranges
+                    if any((e0 % 8) or (e1 % 8) for e0, e1 in self.ranges):
+                        self.passes = None
+
+    def _exchange(self, elem_begin, elem_count, out_elem):
+        """barrier -> reduce+cast of image[elem_begin : elem_begin+elem_count) -> barrier, on the current stream."""
+        from . import capi
+
+        offs = (elem_begin * 4, elem_begin * out_elem)
+        self.h_image.barrier(channel=0)   # every rank's part of the image is complete
+        if self.use_multimem:             # in-switch sum (NVLS): 1/R of the bytes per GPU
+            capi.multimem_reduce_cast(self.mc_image, self.mc_out, self.world, self.rank, elem_count, self.dtype,
+                                      self.device, byte_offsets=offs)
+        else:                             # plain peer loads / stores
+            capi.peer_reduce_cast(self.image_ptrs, self.out_ptrs, self.rank, elem_count, self.dtype, self.device,
+                                  byte_offsets=offs)
+        self.h_out.barrier(channel=0)     # every rank's pushes have landed
+
+    def backward(self, value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_packed=None):
+        from . import capi
+
+        if tuple(value.shape) != self.shape or value.dtype != self.dtype:
+            raise ValueError("PeerReducer was built for another value shape / dtype")
+        B = value.shape[0]
+        if grad_packed is None:
+            grad_packed = torch.empty_like(packed)
+        main = torch.cuda.current_stream(self.device)
+        self.side.wait_stream(main)  # earlier readers of self.out / self.image are done
+        out_elem = self.out.element_size()
+
+        def hand_over(elem_begin, elem_count):
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(self.side):
+                self.side.wait_event(done)
+                self._exchange(elem_begin, elem_count, out_elem)
+
+        def args_of(b):
+            return (value[b:b + 1], shapes, lsi, packed[b:b + 1], grad_out[b:b + 1], K, self.image[b:b + 1],
+                    grad_packed[b:b + 1])
+
+        if self.passes is None:
+            for b in range(B):
+                a = args_of(b)
+                capi.backward_accumulate(*a[:7], grad_packed=a[7], im2col_step=im2col_step)
+                hand_over(b * self.per_batch, self.per_batch)
+        else:
+            # pass-major order: the big level of every batch element first, so that all of its exchanges
+            # hide behind later launches and only the small remainder of the last element is exposed
+            for n, ((lb, le), (e0, e1)) in enumerate(zip(self.passes, self.ranges)):
+                last = n == len(self.passes) - 1
+                flags = (capi.BWD_ZERO_IMAGE if n == 0 else capi.BWD_RESUME) | (capi.BWD_FINALIZE if last else 0)
+                for b in range(B):
+                    capi.backward_accumulate_levels(*args_of(b), lb, le, flags, im2col_step=im2col_step)
+                    hand_over(b * self.per_batch + e0, e1 - e0)
+        main.wait_stream(self.side)
+        return self.out, grad_packed
+
+
 class CudaLocalOps:
     """Per-rank operator on raw device buffers through the C ABI (``libfda_b200.so``)."""
+
+    def __init__(self):
+        self._reducers = {}
+
+    def backward_reduced(self, value, shapes, lsi, packed, grad_out, K, im2col_step, group):
+        """Backward with the cross-rank sum done by ``PeerReducer`` (NVLink peer memory).  Returns
+        ``None`` when ``FDA_SHARDED_REDUCE=nccl`` asks for the plain all-reduce path instead."""
+        import os
+
+        if os.environ.get("FDA_SHARDED_REDUCE", "peer") != "peer":
+            return None
+        key = (tuple(value.shape), value.dtype, value.device, id(group))
+        if key not in self._reducers:
+            self._reducers[key] = PeerReducer(value.shape, value.dtype, value.device, group, spatial_shapes=shapes)
+        gv, gp = self._reducers[key].backward(value, shapes, lsi, packed, grad_out, K, im2col_step)
+        return gv.clone(), gp
 
     def forward(self, value, shapes, lsi, packed, K, im2col_step):
         from . import capi
@@ -56,6 +192,16 @@ class CudaLocalOps:
         return capi.cast_grad_value(accum, torch.empty(accum.shape, dtype=dtype, device=accum.device))
 
 
+_DEFAULT_OPS = None
+
+
+def _default_cuda_ops():
+    global _DEFAULT_OPS
+    if _DEFAULT_OPS is None:
+        _DEFAULT_OPS = CudaLocalOps()
+    return _DEFAULT_OPS
+
+
 class QueryShardedFlashDeformAttnFunction(Function):
     """``apply(value, shapes, level_start_index, packed_shard, im2col_step, K, group, local_ops)``
 
@@ -66,7 +212,7 @@ class QueryShardedFlashDeformAttnFunction(Function):
 
     @staticmethod
     def forward(ctx, value, shapes, lsi, packed_shard, im2col_step, K, group=None, local_ops=None):
-        ops = local_ops if local_ops is not None else CudaLocalOps()
+        ops = local_ops if local_ops is not None else _default_cuda_ops()
         ctx.ops, ctx.group, ctx.K, ctx.im2col_step = ops, group, K, im2col_step
         L = shapes.shape[0]
         if packed_shard.shape[-1] != L * K * 4:
@@ -80,9 +226,15 @@ class QueryShardedFlashDeformAttnFunction(Function):
     @once_differentiable
     def backward(ctx, grad_out):
         value, shapes, lsi, packed_shard = ctx.saved_tensors
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(ctx.group) > 1
+        if multi and hasattr(ctx.ops, "backward_reduced"):
+            fused = ctx.ops.backward_reduced(value, shapes, lsi, packed_shard, grad_out.contiguous(), ctx.K,
+                                             ctx.im2col_step, ctx.group)
+            if fused is not None:
+                return fused[0], None, None, fused[1], None, None, None, None
         accum, grad_packed = ctx.ops.backward_accumulate(
             value, shapes, lsi, packed_shard, grad_out.contiguous(), ctx.K, ctx.im2col_step)
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+        if multi:
             dist.all_reduce(accum, op=dist.ReduceOp.SUM, group=ctx.group)
         return ctx.ops.cast(accum, value.dtype), None, None, grad_packed, None, None, None, None
 

@@ -1,0 +1,73 @@
+"""GPU checks of the multi-GPU pieces: the peer-memory reduce+cast kernel (degenerate world of one on a
+single GPU) and, where two GPUs are visible, the query-sharded operator over NCCL / NVLink peer memory
+against the unsharded operator."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import fda_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_peer_reduce_cast_world_of_one_is_a_cast(dtype):
+    from ops3d_b200 import capi
+
+    image = torch.randn(3, 50, 4, 16, device="cuda")
+    out = torch.empty(image.shape, dtype=dtype, device="cuda")
+    capi.peer_reduce_cast([image.data_ptr()], [out.data_ptr()], 0, image.numel(), dtype, image.device)
+    torch.cuda.synchronize()
+    assert torch.equal(out, image.to(dtype))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, mode, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", FDA_SHARDED_REDUCE=mode)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from ops3d_b200 import FlashDeformAttnFunction
+        from ops3d_b200.sharded import shard_queries, sharded_flash_deform_attn
+
+        shapes = [(8, 16, 32), (4, 8, 16)]
+        K = 4
+        value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, 2, 301, 8, 32, K, seed=31)
+        sh, lsi = sh.to(dev), lsi.to(dev)
+        ok = True
+        for step in range(2):  # twice: buffers of the first backward are reused by the second
+            v = value.to(dev, torch.bfloat16).requires_grad_(True)
+            pk = shard_queries(packed, rank, world).to(dev).requires_grad_(True)
+            out = sharded_flash_deform_attn(v, sh, lsi, pk, 64, K)
+            out.backward(shard_queries(grad_out, rank, world).to(dev, torch.bfloat16))
+            v1 = value.to(dev, torch.bfloat16).requires_grad_(True)
+            pk1 = packed.to(dev).requires_grad_(True)
+            out1 = FlashDeformAttnFunction.apply(v1, sh, lsi, pk1, 64, K, True)
+            out1.backward(grad_out.to(dev, torch.bfloat16))
+            torch.cuda.synchronize()
+            scale = v1.grad.float().abs().max().item()
+            ok &= torch.equal(out, shard_queries(out1, rank, world))
+            ok &= (v.grad.float() - v1.grad.float()).abs().max().item() <= 2e-2 * scale
+            ok &= torch.equal(pk.grad, shard_queries(pk1.grad, rank, world))
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["peer", "nccl"])
+def test_two_gpus_sharded_equals_unsharded(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_worker, args=(2, _free_port(), mode, ret), nprocs=2, join=True)
+    assert dict(ret) == {0: True, 1: True}
