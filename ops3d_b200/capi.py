@@ -10,7 +10,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfda_b200.so")
+LIB_PATH = os.environ.get("FDA_B200_LIBRARY") or os.path.join(_HERE, "libfda_b200.so")  # override: another build of the same ABI
 
 DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 

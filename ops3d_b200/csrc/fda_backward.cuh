@@ -26,10 +26,14 @@
 
 #include "fda_device.cuh"
 
+#ifndef FDA_BWD_MIN_BLOCKS
+#define FDA_BWD_MIN_BLOCKS 2
+#endif
+
 namespace fda {
 
 template <typename VT, typename PT>
-__global__ void __launch_bounds__(kThreads, 2) fda_backward_kernel(const Problem p) {
+__global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_kernel(const Problem p) {
     constexpr int CPL = Vec16<VT>::kCPL;
     constexpr int NRED = CPL / 4;  // 16-byte fp32 reductions per lane and corner
     __shared__ LevelGeom geom[kMaxLevels];

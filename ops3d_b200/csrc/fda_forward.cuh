@@ -17,10 +17,14 @@
 
 #include "fda_device.cuh"
 
+#ifndef FDA_FWD_MIN_BLOCKS
+#define FDA_FWD_MIN_BLOCKS 2
+#endif
+
 namespace fda {
 
 template <typename VT, typename PT, bool kStage>
-__global__ void __launch_bounds__(kThreads, 2) fda_forward_kernel(const Problem p) {
+__global__ void __launch_bounds__(kThreads, FDA_FWD_MIN_BLOCKS) fda_forward_kernel(const Problem p) {
     constexpr int CPL = Vec16<VT>::kCPL;
     __shared__ LevelGeom geom[kMaxLevels];
     extern __shared__ __align__(16) float smem_tile[];
