@@ -280,6 +280,9 @@ def run_ours(args, cfg):
     use_peer = world > 1 and args.reduce == "peer"
     reducer = PeerReducer(value.shape, vdt, dev, spatial_shapes=shapes) if use_peer else None
     reducer_passes = reducer.passes if use_peer else None
+    L = len(cfg["shapes"])
+    n_scratch = capi.scratch_bytes(value, packed, K)
+    scratch = torch.empty(n_scratch, dtype=torch.uint8, device=dev) if (n_scratch and not use_peer) else None
     accum = None
     if not use_peer:
         accum = torch.empty(value.shape, dtype=torch.float32, device=dev) if vdt != torch.float32 else grad_value
@@ -293,7 +296,8 @@ def run_ours(args, cfg):
             reducer.backward(value, shapes, lsi, packed, grad_out, K, grad_packed=grad_packed)
             if ev: ev[2].record(); ev[3].record()
             return
-        capi.backward_accumulate(value, shapes, lsi, packed, grad_out, K, accum, grad_packed=grad_packed)
+        capi.backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, grad_packed, 0, L,
+                                        capi.BWD_ZERO_IMAGE | capi.BWD_FINALIZE, scratch=scratch)
         if ev: ev[2].record()
         if world > 1:
             dist.all_reduce(accum)
@@ -338,7 +342,7 @@ def run_ours(args, cfg):
         host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (out, grad_value, grad_packed)]
         h2d = sum(t.numel() * t.element_size() for t in host_in)
         d2h = sum(t.numel() * t.element_size() for t in host_out)
-        del out, grad_value, grad_packed, accum, reducer
+        del out, grad_value, grad_packed, accum, reducer, scratch
         torch.cuda.empty_cache()
 
         def e2e_step():

@@ -89,11 +89,20 @@ int fda_forward(const void *value, const int64_t *spatial_shapes, const int64_t 
                 int im2col_step, int d_stride, int block_thread, int use_reg, void *stream);
 
 /*
- * Bytes of device workspace fda_backward needs for this problem (0 for an fp32 value: the
- * scatter then accumulates straight into grad_value).  For 16-bit values it is the fp32
- * accumulation image of grad_value, batch*num_value*num_heads*head_dim*4 bytes.
+ * Bytes of device workspace fda_backward needs for this problem: the fp32 accumulation image of
+ * grad_value for 16-bit values (batch*num_value*num_heads*head_dim*4, rounded up to 256; none for
+ * an fp32 value, which accumulates in place) plus fda_backward_scratch_bytes().
  */
-size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int value_dtype);
+size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int num_query,
+                                    int num_points, int value_dtype);
+
+/*
+ * Bytes of scratch for the slab-binned handling of the largest pyramid level: slab counters plus
+ * one 8-byte entry per (row, point) of one level.  0 when binning cannot pay off (the gradient
+ * image of one batch element fits the device's L2 budget) or is switched off (FDA_BINNING=0).
+ * Without scratch the backward still works, through the plain scatter kernel alone.
+ */
+size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_query, int num_points);
 
 /*
  * Backward: grad_value (scatter-add of softmax_i * w_corner * grad_output through fp32 vector
@@ -107,8 +116,10 @@ size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int
  * chunk loop and cast-back of flash_deform_attn_cuda_backward, csrc/cuda/flash_deform_attn_cuda.cu:125-178.
  *
  * The library zero-fills what it accumulates into (workspace, or grad_value for fp32); both
- * outputs are fully written.  workspace must be 16-byte aligned and at least
- * fda_backward_workspace_bytes() long; it may be NULL when that is 0.
+ * outputs are fully written.  workspace must be 256-byte aligned and at least
+ * fda_backward_workspace_bytes() long; it may be NULL when that is 0.  When the gradient image
+ * of one batch element does not fit L2, the largest level is processed slab by slab (its points
+ * are first sorted into z-slabs in the workspace) so that its part of the image stays L2-resident.
  */
 int fda_backward(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
                  const void *sampling_loc_attn, const void *grad_output,
@@ -145,6 +156,8 @@ int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_element
  *   last launch    flags = FDA_BWD_RESUME | FDA_BWD_FINALIZE
  * (a single launch over all levels uses FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE).  Between launches
  * grad_sampling_loc_attn holds intermediate values; it is final after the FINALIZE launch.
+ * scratch (fda_backward_scratch_bytes() bytes, 256-byte aligned, may be NULL) enables the
+ * slab-binned path for the largest level when it is part of the range.
  * No counterpart in the reference.
  */
 #define FDA_BWD_ZERO_IMAGE 1
@@ -155,7 +168,8 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
                                    float *accum, void *grad_sampling_loc_attn,
                                    int batch, int num_value, int num_heads, int head_dim, int num_levels,
                                    int num_query, int num_points, int value_dtype, int packed_dtype,
-                                   int im2col_step, int level_begin, int level_end, int flags, void *stream);
+                                   int im2col_step, int level_begin, int level_end, int flags,
+                                   void *scratch, size_t scratch_bytes, void *stream);
 
 /*
  * Cross-GPU sum + cast of the fp32 images over peer (NVLink) memory, for the query-sharded

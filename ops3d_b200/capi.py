@@ -16,7 +16,7 @@ DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 EXPORTS = (
     "fda_status_string", "fda_last_cuda_error", "fda_version", "fda_forward",
-    "fda_backward_workspace_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
+    "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
 )
 BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE = 1, 2, 4
@@ -46,13 +46,15 @@ def load() -> ctypes.CDLL:
     lib.fda_version.restype = i
     lib.fda_forward.argtypes = [vp] * 5 + [i] * 13 + [vp]
     lib.fda_forward.restype = i
-    lib.fda_backward_workspace_bytes.argtypes = [i] * 5
+    lib.fda_backward_workspace_bytes.argtypes = [i] * 7
+    lib.fda_backward_scratch_bytes.argtypes = [i] * 6
+    lib.fda_backward_scratch_bytes.restype = sz
     lib.fda_backward_workspace_bytes.restype = sz
     lib.fda_backward.argtypes = [vp] * 8 + [sz] + [i] * 12 + [vp]
     lib.fda_backward.restype = i
     lib.fda_backward_accumulate.argtypes = [vp] * 7 + [i] * 10 + [vp]
     lib.fda_backward_accumulate.restype = i
-    lib.fda_backward_accumulate_levels.argtypes = [vp] * 7 + [i] * 13 + [vp]
+    lib.fda_backward_accumulate_levels.argtypes = [vp] * 7 + [i] * 13 + [vp, sz, vp]
     lib.fda_backward_accumulate_levels.restype = i
     lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
     lib.fda_cast_grad_value.restype = i
@@ -96,9 +98,14 @@ def forward(value, shapes, lsi, packed, K, im2col_step=64, use_reg=True, out=Non
     return out
 
 
-def workspace_bytes(value) -> int:
+def workspace_bytes(value, packed, K) -> int:
     B, N, G, D = value.shape
-    return int(load().fda_backward_workspace_bytes(B, N, G, D, DTYPE_CODE[value.dtype]))
+    return int(load().fda_backward_workspace_bytes(B, N, G, D, packed.shape[1], K, DTYPE_CODE[value.dtype]))
+
+
+def scratch_bytes(value, packed, K) -> int:
+    B, N, G, D = value.shape
+    return int(load().fda_backward_scratch_bytes(B, N, G, D, packed.shape[1], K))
 
 
 def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value=None, grad_packed=None,
@@ -109,9 +116,9 @@ def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value
         grad_value = torch.empty_like(value)
     if grad_packed is None:
         grad_packed = torch.empty_like(packed)
-    need = workspace_bytes(value)
+    need = workspace_bytes(value, packed, K)
     if need and workspace is None:
-        workspace = torch.empty(need // 4, dtype=torch.float32, device=value.device)
+        workspace = torch.empty((need + 3) // 4, dtype=torch.float32, device=value.device)
     with torch.cuda.device(value.device):
         check(load().fda_backward(
             value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
@@ -137,15 +144,18 @@ def backward_accumulate(value, shapes, lsi, packed, grad_out, K, accum, grad_pac
 
 
 def backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, grad_packed, level_begin, level_end,
-                               flags, im2col_step=64):
-    """``fda_backward_accumulate_levels``: one launch over the levels ``[level_begin, level_end)``."""
+                               flags, im2col_step=64, scratch=None):
+    """``fda_backward_accumulate_levels``: one launch over the levels ``[level_begin, level_end)``.
+    ``scratch`` (a tensor of at least ``scratch_bytes()`` bytes) enables the slab-binned path."""
     B, N, G, D, L, Q = _dims(value, shapes, packed)
     with torch.cuda.device(value.device):
         check(load().fda_backward_accumulate_levels(
             value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
             accum.data_ptr(), grad_packed.data_ptr(),
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype], im2col_step,
-            level_begin, level_end, flags, _stream(value)))
+            level_begin, level_end, flags,
+            scratch.data_ptr() if scratch is not None else None,
+            scratch.numel() * scratch.element_size() if scratch is not None else 0, _stream(value)))
     return grad_packed
 
 

@@ -109,11 +109,11 @@ std::vector<at::Tensor> flash_deform_attn_backward(const at::Tensor &value, cons
     if (d.Q == 0 || d.B == 0) return {at::zeros_like(value), at::zeros_like(sampling_loc_attn)};
     at::Tensor grad_value = at::empty_like(value);
     at::Tensor grad_packed = at::empty_like(sampling_loc_attn);
-    const size_t ws_bytes = fda_backward_workspace_bytes(d.B, d.N, d.G, d.D, vdt);
+    const size_t ws_bytes = fda_backward_workspace_bytes(d.B, d.N, d.G, d.D, d.Q, K, vdt);
     at::Tensor workspace;
     void *ws_ptr = nullptr;
     if (ws_bytes > 0) {
-        workspace = at::empty({(int64_t)(ws_bytes / sizeof(float))}, value.options().dtype(at::kFloat));
+        workspace = at::empty({(int64_t)((ws_bytes + 3) / sizeof(float))}, value.options().dtype(at::kFloat));
         ws_ptr = workspace.data_ptr();
     }
     const int rc = fda_backward(value.data_ptr(), spatial_shapes.data_ptr<int64_t>(), level_start_index.data_ptr<int64_t>(),

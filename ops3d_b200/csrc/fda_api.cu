@@ -10,6 +10,7 @@
 #include <utility>
 
 #include "fda_backward.cuh"
+#include "fda_backward_binned.cuh"
 #include "fda_forward.cuh"
 
 namespace {
@@ -51,8 +52,14 @@ int validate(const Shape &s, int im2col_step) {
 unsigned long long l2_keep_budget() {
     static std::mutex mu;
     static std::map<int, int> l2_bytes;
+    double frac = 0.7;
+    if (const char *e = std::getenv("FDA_L2_KEEP_FRACTION")) frac = std::atof(e);
+    if (frac < 0) frac = 0;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {  // no device (sizing queries on a build machine): B200's 126 MB
+        (void)cudaGetLastError();
+        return (unsigned long long)(frac * 126.0 * 1024 * 1024);
+    }
     int l2 = 0;
     {
         std::lock_guard<std::mutex> lock(mu);
@@ -64,9 +71,6 @@ unsigned long long l2_keep_budget() {
             l2 = it->second;
         }
     }
-    double frac = 0.7;
-    if (const char *e = std::getenv("FDA_L2_KEEP_FRACTION")) frac = std::atof(e);
-    if (frac < 0) frac = 0;
     return (unsigned long long)(frac * (double)l2);
 }
 
@@ -84,6 +88,8 @@ fda::Problem make_problem(const Shape &s) {
     p.GD = s.G * s.D;
     p.value_elem_bytes = dtype_size(s.vdt);
     p.l2_keep_bytes = l2_keep_budget();
+    p.level_mask = (1 << s.L) - 1;
+    p.finalize = 1;
     return p;
 }
 
@@ -150,8 +156,40 @@ int launch_forward(fda::Problem p, bool stage, cudaStream_t st) {
     return e == cudaSuccess ? FDA_OK : cuda_fail(e);
 }
 
+inline size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+// Scratch of the slab-binned path: counters [3][B][kMaxSlabs] then entries [B][rows_per_b*K] (8 bytes each).
+// Zero when binning cannot apply to this problem (image of one batch element fits the L2 budget, or
+// the entry index would not fit 32 bits, or FDA_BINNING=0).
+size_t bin_scratch_bytes(int B, int N, int G, int D, int Q, int K) {
+    if (const char *e = std::getenv("FDA_BINNING")) if (std::atoi(e) == 0) return 0;
+    if (B <= 0 || N <= 0 || G <= 0 || D <= 0 || Q <= 0 || K <= 0 || K > 8) return 0;
+    if ((unsigned long long)N * G * D * 4ull <= l2_keep_budget()) return 0;
+    const unsigned long long cap = (unsigned long long)Q * G * K;
+    if (cap >= (1ull << 32)) return 0;
+    return round256((size_t)3 * B * fda::kMaxSlabs * sizeof(unsigned int)) + (size_t)B * cap * sizeof(uint2);
+}
+
+template <typename VT, typename PT>
+int launch_binned(fda::Problem p, cudaStream_t st) {
+    const size_t counter_bytes = (size_t)3 * p.B * fda::kMaxSlabs * sizeof(unsigned int);
+    cudaError_t e = cudaMemsetAsync(p.bin_counters, 0, counter_bytes, st);
+    if (e != cudaSuccess) return cuda_fail(e);
+    const dim3 rows_grid((unsigned)((p.rows_per_b + 255) / 256), (unsigned)p.B, 1);
+    fda::fda_bin_count_kernel<PT><<<rows_grid, 256, 0, st>>>(p);
+    fda::fda_bin_scan_kernel<<<(unsigned)((p.B + 127) / 128), 128, 0, st>>>(p);
+    fda::fda_bin_fill_kernel<PT><<<rows_grid, 256, 0, st>>>(p);
+    // x: blocks striding over one slab's list; y: slab (slabs run one after the other); z: batch element
+    const dim3 grid(592, fda::kMaxSlabs, (unsigned)p.B);
+    fda::fda_backward_binned_kernel<VT, PT><<<grid, fda::kThreads, 0, st>>>(p);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? FDA_OK : cuda_fail(e);
+}
+
 template <typename VT, typename PT>
 int launch_backward(fda::Problem p, cudaStream_t st) {
+    if (p.bin_allowed)
+        if (int rc = launch_binned<VT, PT>(p, st)) return rc;
     p.row_stride = padded_stride(5 * p.LK);
     const int threads = pick_threads(p, p.row_stride);
     const size_t smem = (size_t)(threads >> p.gs_log2) * p.row_stride * sizeof(float);
@@ -218,10 +256,15 @@ int fda_forward(const void *value, const int64_t *spatial_shapes, const int64_t 
     return FDA_DISPATCH(value_dtype, packed_dtype, (launch_forward<VT, PT>(p, stage, static_cast<cudaStream_t>(stream))));
 }
 
-size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int value_dtype) {
-    if (value_dtype == FDA_DTYPE_F32) return 0;
+size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int num_query,
+                                    int num_points, int value_dtype) {
     if (batch <= 0 || num_value <= 0 || num_heads <= 0 || head_dim <= 0) return 0;
-    return (size_t)batch * num_value * num_heads * head_dim * sizeof(float);
+    const size_t image = value_dtype == FDA_DTYPE_F32 ? 0 : round256((size_t)batch * num_value * num_heads * head_dim * sizeof(float));
+    return image + bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points);
+}
+
+size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_query, int num_points) {
+    return bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points);
 }
 
 int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
@@ -229,7 +272,8 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
                                    float *accum, void *grad_sampling_loc_attn,
                                    int batch, int num_value, int num_heads, int head_dim, int num_levels,
                                    int num_query, int num_points, int value_dtype, int packed_dtype,
-                                   int im2col_step, int level_begin, int level_end, int flags, void *stream) {
+                                   int im2col_step, int level_begin, int level_end, int flags,
+                                   void *scratch, size_t scratch_bytes, void *stream) {
     if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !grad_output || !accum || !grad_sampling_loc_attn)
         return FDA_ERR_NULL_POINTER;
     const Shape s{batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, packed_dtype};
@@ -247,11 +291,22 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
     fda::Problem p = make_problem(s);
     p.value = value; p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn;
     p.grad_out = grad_output; p.accum = accum; p.grad_packed = grad_sampling_loc_attn;
-    const int chunks_per_level = num_points / 4;
-    p.chunk_begin = level_begin * chunks_per_level;
-    p.chunk_end = level_end * chunks_per_level;
+    p.level_mask = ((1 << level_end) - 1) & ~((1 << level_begin) - 1);
     p.resume = (flags & FDA_BWD_RESUME) ? 1 : 0;
     p.finalize = (flags & FDA_BWD_FINALIZE) ? 1 : 0;
+    // slab-binned handling of the largest level, when the caller gave scratch for it
+    const size_t need = bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points);
+    if (need > 0 && scratch && scratch_bytes >= need && aligned16(scratch)) {
+        p.bin_allowed = 1;
+        p.bin_counters = static_cast<unsigned int *>(scratch);
+        p.bin_entries = reinterpret_cast<uint2 *>(static_cast<char *>(scratch) +
+                                                  round256((size_t)3 * batch * fda::kMaxSlabs * sizeof(unsigned int)));
+        p.bin_cap = (unsigned long long)num_query * num_heads * num_points;
+        double slab_mb = 16.0;  // share of the fp32 image per slab (value rows of the slab add half of that); 8-16 MB measured best on B200
+        if (const char *e = std::getenv("FDA_BIN_SLAB_MB")) slab_mb = std::atof(e);
+        p.bin_slab_bytes = (unsigned long long)(slab_mb * 1048576.0);
+        if (p.bin_slab_bytes < 4096) p.bin_slab_bytes = 4096;
+    }
     return FDA_DISPATCH(value_dtype, packed_dtype, (launch_backward<VT, PT>(p, st)));
 }
 
@@ -264,7 +319,8 @@ int fda_backward_accumulate(const void *value, const int64_t *spatial_shapes, co
     return fda_backward_accumulate_levels(value, spatial_shapes, level_start_index, sampling_loc_attn, grad_output, accum,
                                           grad_sampling_loc_attn, batch, num_value, num_heads, head_dim, num_levels,
                                           num_query, num_points, value_dtype, packed_dtype, im2col_step, 0,
-                                          num_levels > 0 ? num_levels : 1, FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE, stream);
+                                          num_levels > 0 ? num_levels : 1, FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE,
+                                          nullptr, 0, stream);
 }
 
 int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_elements, int value_dtype, void *stream) {
@@ -300,18 +356,21 @@ int fda_backward(const void *value, const int64_t *spatial_shapes, const int64_t
                  int im2col_step, int d_stride, int block_thread, void *stream) {
     (void)d_stride; (void)block_thread;
     if (!grad_value) return FDA_ERR_NULL_POINTER;
-    const size_t need = fda_backward_workspace_bytes(batch, num_value, num_heads, head_dim, value_dtype);
+    const size_t need = fda_backward_workspace_bytes(batch, num_value, num_heads, head_dim, num_query, num_points, value_dtype);
+    const size_t n = (size_t)batch * num_value * num_heads * head_dim;
+    const size_t image_bytes = value_dtype == FDA_DTYPE_F32 ? 0 : round256(n * sizeof(float));
     float *accum = static_cast<float *>(grad_value);
-    if (need > 0) {
-        if (!workspace || workspace_bytes < need) return FDA_ERR_WORKSPACE;
-        accum = static_cast<float *>(workspace);
-    }
+    if (need > 0 && (!workspace || workspace_bytes < need)) return FDA_ERR_WORKSPACE;
+    if (image_bytes > 0) accum = static_cast<float *>(workspace);
+    void *scratch = need > image_bytes ? static_cast<char *>(workspace) + image_bytes : nullptr;
     if (!aligned16(grad_value)) return FDA_ERR_MISALIGNED;
-    int rc = fda_backward_accumulate(value, spatial_shapes, level_start_index, sampling_loc_attn, grad_output, accum,
-                                     grad_sampling_loc_attn, batch, num_value, num_heads, head_dim, num_levels,
-                                     num_query, num_points, value_dtype, packed_dtype, im2col_step, stream);
-    if (rc != FDA_OK || need == 0) return rc;
-    return fda_cast_grad_value(accum, grad_value, (size_t)batch * num_value * num_heads * head_dim, value_dtype, stream);
+    int rc = fda_backward_accumulate_levels(value, spatial_shapes, level_start_index, sampling_loc_attn, grad_output, accum,
+                                            grad_sampling_loc_attn, batch, num_value, num_heads, head_dim, num_levels,
+                                            num_query, num_points, value_dtype, packed_dtype, im2col_step, 0,
+                                            num_levels > 0 ? num_levels : 1, FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE,
+                                            scratch, need - image_bytes, stream);
+    if (rc != FDA_OK || image_bytes == 0) return rc;
+    return fda_cast_grad_value(accum, grad_value, n, value_dtype, stream);
 }
 
 }  // extern "C"

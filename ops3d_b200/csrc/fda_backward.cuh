@@ -16,12 +16,12 @@
 //   * soft-max backward in closed form, grad_logit_i = p_i * (dalpha_i - sum_j p_j dalpha_j),
 //     instead of the reference's O((L*K)^2) Jacobian loop (:413-427).
 //
-// A launch may cover only a range of pyramid levels (4-point chunks [chunk_begin, chunk_end) of
-// every row).  A non-final launch leaves the raw dalpha of its points in the logit slots of
-// grad_packed; the final launch (`resume`) picks up the finished slots of the other chunks from
-// grad_packed, adds its own and applies the soft-max backward over all points.  This lets a
-// multi-GPU caller finish the largest level first and exchange its part of the gradient image
-// while the remaining levels are still being computed.
+// A launch may cover only some pyramid levels (level_mask).  A non-final launch leaves the raw
+// dalpha of its points in the logit slots of grad_packed; the final launch (`resume`) picks up
+// the finished slots of the other levels from grad_packed, adds its own and applies the soft-max
+// backward over all points.  This lets a multi-GPU caller finish the largest level first and
+// exchange its part of the gradient image while the remaining levels are still being computed,
+// and lets the largest level be handled slab by slab (fda_backward_binned.cuh).
 #pragma once
 
 #include "fda_device.cuh"
@@ -32,15 +32,101 @@
 
 namespace fda {
 
+// grad_output of one row as seen by one lane: its gather channels (for the dot products) and its
+// scatter channels (4*lane_c + r*4*lpg, so that the lanes of a row cover contiguous bytes).
+template <typename VT>
+struct RowGrad {
+    static constexpr int CPL = Vec16<VT>::kCPL;
+    static constexpr int NRED = CPL / 4;
+    float d[CPL];
+    float s[NRED][4];
+    __device__ __forceinline__ void load(const VT *go_row, int lane_c, int lpg, bool active, uint64_t pol) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (active) raw = ldg16_hint(go_row + (size_t)lane_c * CPL, pol);
+        Vec16<VT>::unpack(raw, d);
+#pragma unroll
+        for (int r = 0; r < NRED; ++r) {
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (active) f = load4<VT>(go_row + r * 4 * lpg + 4 * lane_c);
+            s[r][0] = f.x; s[r][1] = f.y; s[r][2] = f.z; s[r][3] = f.w;
+        }
+    }
+};
+
+// Backward of one sampling point for the lanes of one row: gathers the 8 corners, scatters
+// a*w*grad_out into the fp32 image, and returns (summed over the row's lanes) the gradients w.r.t.
+// the normalised coordinates and dalpha = <sample, grad_out>.  Must be called by all 32 lanes.
+template <typename VT>
+__device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, float x, float y, float z, float a,
+                                               const VT *lvl, float *acc_lvl, const RowGrad<VT> &go, int red_stride,
+                                               bool active, int gs, uint64_t pol_v, uint64_t pol_g,
+                                               float &gx_out, float &gy_out, float &gz_out, float &da_out) {
+    constexpr int CPL = Vec16<VT>::kCPL;
+    constexpr int NRED = CPL / 4;
+    PointGeom pg;
+    point_geometry(lv, GD, x, y, z, pg);
+    uint4 raw[8];
+    bool in[8];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        in[n] = active && pg.zin[n >> 2] && pg.yin[(n >> 1) & 1] && pg.xin[n & 1];
+        raw[n] = in[n] ? ldg16_hint(lvl + pg.off[n], pol_v) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float dot[8];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        const float w = (pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2];
+        const float aw = a * w;
+        if (in[n]) {
+            float *dst = acc_lvl + pg.off[n];
+#pragma unroll
+            for (int r = 0; r < NRED; ++r)
+                red_add_f32x4_hint(dst + r * red_stride, aw * go.s[r][0], aw * go.s[r][1], aw * go.s[r][2], aw * go.s[r][3], pol_g);
+        }
+        float v[CPL];
+        Vec16<VT>::unpack(raw[n], v);
+        float d = 0.f;
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) d = fmaf(v[k], go.d[k], d);
+        dot[n] = d;  // 0 for corners outside the level
+    }
+    // d out / d x_im = sum_{z,y} wz*wy*(dot[z,y,1] - dot[z,y,0]), likewise y and z; dalpha = sum w*dot
+    const float wzy[4] = {pg.wz[0] * pg.wy[0], pg.wz[0] * pg.wy[1], pg.wz[1] * pg.wy[0], pg.wz[1] * pg.wy[1]};
+    const float wzx[4] = {pg.wz[0] * pg.wx[0], pg.wz[0] * pg.wx[1], pg.wz[1] * pg.wx[0], pg.wz[1] * pg.wx[1]};
+    const float wyx[4] = {pg.wy[0] * pg.wx[0], pg.wy[0] * pg.wx[1], pg.wy[1] * pg.wx[0], pg.wy[1] * pg.wx[1]};
+    float gx = wzy[0] * (dot[1] - dot[0]) + wzy[1] * (dot[3] - dot[2]) + wzy[2] * (dot[5] - dot[4]) + wzy[3] * (dot[7] - dot[6]);
+    float gy = wzx[0] * (dot[2] - dot[0]) + wzx[1] * (dot[3] - dot[1]) + wzx[2] * (dot[6] - dot[4]) + wzx[3] * (dot[7] - dot[5]);
+    float gz = wyx[0] * (dot[4] - dot[0]) + wyx[1] * (dot[5] - dot[1]) + wyx[2] * (dot[6] - dot[2]) + wyx[3] * (dot[7] - dot[3]);
+    float da = 0.f;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) da = fmaf((pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2], dot[n], da);
+    for (int mask = gs >> 1; mask > 0; mask >>= 1) {
+        gx += __shfl_xor_sync(0xffffffffu, gx, mask);
+        gy += __shfl_xor_sync(0xffffffffu, gy, mask);
+        gz += __shfl_xor_sync(0xffffffffu, gz, mask);
+        da += __shfl_xor_sync(0xffffffffu, da, mask);
+    }
+    gx_out = a * (float)lv.W * gx;
+    gy_out = a * (float)lv.H * gy;
+    gz_out = a * (float)lv.D * gz;
+    da_out = da;
+}
+
 template <typename VT, typename PT>
 __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_kernel(const Problem p) {
     constexpr int CPL = Vec16<VT>::kCPL;
-    constexpr int NRED = CPL / 4;  // 16-byte fp32 reductions per lane and corner
     __shared__ LevelGeom geom[kMaxLevels];
+    __shared__ int s_mask, s_resume;
     extern __shared__ __align__(16) float smem_tile[];
 
     const int tid = threadIdx.x;
-    if (tid == 0) build_level_table(geom, p.shapes, p.lsi, p.L, p.GD, p.value_elem_bytes, true, p.l2_keep_bytes);
+    if (tid == 0) {
+        build_level_table(geom, p.shapes, p.lsi, p.L, p.GD, p.value_elem_bytes, true, p.l2_keep_bytes);
+        // the slab-binned launches of this call (if any) own the largest level
+        const BinPlan plan = make_bin_plan(p);
+        s_mask = plan.enabled ? (p.level_mask & ~(1 << plan.level)) : p.level_mask;
+        s_resume = p.resume | plan.enabled;
+    }
     const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
 
     const int b = blockIdx.y;
@@ -64,6 +150,8 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
     stage_rows<PT>(static_cast<const PT *>(p.packed) + warp_elem0, wtile, nrows, LK, p.row_stride, lane);
     float *trow = wtile + (lane >> p.gs_log2) * p.row_stride;
     __syncthreads();  // level table and this warp's tile visible
+    const int level_mask = s_mask;
+    if (level_mask == 0 && !p.finalize) return;  // nothing left for this launch (uniform over the grid)
 
     const int nchunk = LK >> 2;
     float m = -INFINITY;
@@ -80,15 +168,15 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
     }
     const float inv = 1.0f / s;
     __syncwarp();
-    if (p.resume) {
-        // slots of chunks handled by an earlier launch: finished coordinate gradients and raw dalpha
+    if (s_resume) {
+        // slots of levels handled by an earlier launch: finished coordinate gradients and raw dalpha
         const PT *prev = static_cast<const PT *>(p.grad_packed) + warp_elem0;
         const int nvec = nrows * LK;
         for (int v = lane; v < nvec; v += 32) {
             const int r = v / LK;
             const int c = (v - r * LK) * 4;
             const int j = c < 3 * LK ? c / 12 : (c - 3 * LK) >> 2;
-            if (j < p.chunk_begin || j >= p.chunk_end)
+            if (!((level_mask >> (j >> p.k_shift)) & 1))
                 *reinterpret_cast<float4 *>(wtile + r * p.row_stride + c) = load4_stream<PT>(prev + (size_t)v * 4);
         }
         __syncwarp();
@@ -99,25 +187,13 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
     const VT *value_b = static_cast<const VT *>(p.value) + head_elem + (size_t)lane_c * CPL;
     float *accum_b = p.accum + head_elem + (size_t)lane_c * 4;
 
-    // grad_output of this row: the lane's gather channels (for the dot products) and its
-    // scatter channels (4*lane_c + j*4*lpg, so that the lanes of a row cover contiguous bytes).
-    float go_d[CPL];
-    float go_s[NRED][4];
-    {
-        const VT *go_row = static_cast<const VT *>(p.grad_out) + ((size_t)b * p.rows_per_b + (row_ok ? row : 0)) * (size_t)p.D;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (active) raw = ldg16_hint(go_row + (size_t)lane_c * CPL, pol_stream);
-        Vec16<VT>::unpack(raw, go_d);
-#pragma unroll
-        for (int r = 0; r < NRED; ++r) {
-            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (active) f = load4<VT>(go_row + r * 4 * p.lpg + 4 * lane_c);
-            go_s[r][0] = f.x; go_s[r][1] = f.y; go_s[r][2] = f.z; go_s[r][3] = f.w;
-        }
-    }
+    RowGrad<VT> go;
+    go.load(static_cast<const VT *>(p.grad_out) + ((size_t)b * p.rows_per_b + (row_ok ? row : 0)) * (size_t)p.D,
+            lane_c, p.lpg, active, pol_stream);
     const int red_stride = 4 * p.lpg;
 
-    for (int j = p.chunk_begin; j < p.chunk_end; ++j) {
+    for (int j = 0; j < nchunk; ++j) {
+        if (!((level_mask >> (j >> p.k_shift)) & 1)) continue;
         const float4 c0 = *reinterpret_cast<const float4 *>(trow + 12 * j);
         const float4 c1 = *reinterpret_cast<const float4 *>(trow + 12 * j + 4);
         const float4 c2 = *reinterpret_cast<const float4 *>(trow + 12 * j + 8);
@@ -133,56 +209,9 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
         const uint64_t pol_g = (lv.keep & 2) ? pol_keep : pol_stream;
         float gxs[4], gys[4], gzs[4], das[4];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const float a = es[t] * inv;
-            PointGeom pg;
-            point_geometry(lv, p.GD, xs[t], ys[t], zs[t], pg);
-            uint4 raw[8];
-            bool in[8];
-#pragma unroll
-            for (int n = 0; n < 8; ++n) {
-                in[n] = active && pg.zin[n >> 2] && pg.yin[(n >> 1) & 1] && pg.xin[n & 1];
-                raw[n] = in[n] ? ldg16_hint(lvl + pg.off[n], pol_v) : make_uint4(0u, 0u, 0u, 0u);
-            }
-            float dot[8];
-#pragma unroll
-            for (int n = 0; n < 8; ++n) {
-                const float w = (pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2];
-                const float aw = a * w;
-                if (in[n]) {
-                    float *dst = acc_lvl + pg.off[n];
-#pragma unroll
-                    for (int r = 0; r < NRED; ++r)
-                        red_add_f32x4_hint(dst + r * red_stride, aw * go_s[r][0], aw * go_s[r][1], aw * go_s[r][2], aw * go_s[r][3], pol_g);
-                }
-                float v[CPL];
-                Vec16<VT>::unpack(raw[n], v);
-                float d = 0.f;
-#pragma unroll
-                for (int k = 0; k < CPL; ++k) d = fmaf(v[k], go_d[k], d);
-                dot[n] = d;  // 0 for corners outside the level
-            }
-            // d out / d x_im = sum_{z,y} wz*wy*(dot[z,y,1] - dot[z,y,0]), likewise y and z; dalpha = sum w*dot
-            const float wzy[4] = {pg.wz[0] * pg.wy[0], pg.wz[0] * pg.wy[1], pg.wz[1] * pg.wy[0], pg.wz[1] * pg.wy[1]};
-            const float wzx[4] = {pg.wz[0] * pg.wx[0], pg.wz[0] * pg.wx[1], pg.wz[1] * pg.wx[0], pg.wz[1] * pg.wx[1]};
-            const float wyx[4] = {pg.wy[0] * pg.wx[0], pg.wy[0] * pg.wx[1], pg.wy[1] * pg.wx[0], pg.wy[1] * pg.wx[1]};
-            float gx = wzy[0] * (dot[1] - dot[0]) + wzy[1] * (dot[3] - dot[2]) + wzy[2] * (dot[5] - dot[4]) + wzy[3] * (dot[7] - dot[6]);
-            float gy = wzx[0] * (dot[2] - dot[0]) + wzx[1] * (dot[3] - dot[1]) + wzx[2] * (dot[6] - dot[4]) + wzx[3] * (dot[7] - dot[5]);
-            float gz = wyx[0] * (dot[4] - dot[0]) + wyx[1] * (dot[5] - dot[1]) + wyx[2] * (dot[6] - dot[2]) + wyx[3] * (dot[7] - dot[3]);
-            float da = 0.f;
-#pragma unroll
-            for (int n = 0; n < 8; ++n) da = fmaf((pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2], dot[n], da);
-            for (int mask = gs >> 1; mask > 0; mask >>= 1) {
-                gx += __shfl_xor_sync(0xffffffffu, gx, mask);
-                gy += __shfl_xor_sync(0xffffffffu, gy, mask);
-                gz += __shfl_xor_sync(0xffffffffu, gz, mask);
-                da += __shfl_xor_sync(0xffffffffu, da, mask);
-            }
-            gxs[t] = a * (float)lv.W * gx;
-            gys[t] = a * (float)lv.H * gy;
-            gzs[t] = a * (float)lv.D * gz;
-            das[t] = da;
-        }
+        for (int t = 0; t < 4; ++t)
+            point_backward<VT>(lv, p.GD, xs[t], ys[t], zs[t], es[t] * inv, lvl, acc_lvl, go, red_stride, active, gs,
+                               pol_v, pol_g, gxs[t], gys[t], gzs[t], das[t]);
         __syncwarp();  // every lane of the row has read this chunk's coordinates
         if (lane_c == 0) {
             *reinterpret_cast<float4 *>(trow + 12 * j) = make_float4(gxs[0], gys[0], gzs[0], gxs[1]);

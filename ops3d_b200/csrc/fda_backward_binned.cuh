@@ -1,0 +1,237 @@
+// Slab-binned backward for the largest pyramid level.
+//
+// Why: with sampling points spread over the whole volume, the scatter into the fp32 image of the
+// largest level (537 MB per batch element at 32x64x256 cells, 8 heads x 32 channels) misses L2 on
+// nearly every corner: a 128-byte read-modify-write through HBM per corner, which is what bounds
+// the plain kernel.  Here the points of that level are first sorted into z-slabs whose share of the
+// image (and of value) fits L2 comfortably; then the slabs are processed one after the other, so
+// gathers and reductions of a slab hit L2 and every image line goes to HBM once.
+//
+//   fda_bin_count_kernel   one thread per row: which slab does each of the level's K points fall in;
+//                          block histogram in shared memory, one global atomic per slab and block
+//   fda_bin_scan_kernel    exclusive scan of the slab counts of every batch element
+//   fda_bin_fill_kernel    one thread per row: soft-max of the row, then appends {row*K+k, probability}
+//                          to the point's slab list (block-local positions from shared-memory atomics,
+//                          one global reservation per slab and block); points with no corner inside the
+//                          level get their zero gradients written here
+//   fda_backward_binned_kernel  grid (x, slab, batch): one lane group per list entry -- dense work,
+//                          no divergence; same point_backward as the plain kernel; writes the point's
+//                          coordinate gradients and raw dalpha straight into grad_packed
+//
+// The remaining levels, and the soft-max backward over all points, are done afterwards by
+// fda_backward_kernel with `resume`.  Nothing here waits on another block.
+#pragma once
+
+#include "fda_backward.cuh"
+
+namespace fda {
+
+// slab of a point from its normalised coordinates, or -1 when no corner lies inside the level
+__device__ __forceinline__ int slab_of_point(const LevelGeom &lv, const BinPlan &plan, float x, float y, float z) {
+    const float xf = floorf(unnormalize(x, (float)lv.W));
+    const float yf = floorf(unnormalize(y, (float)lv.H));
+    const float zf = floorf(unnormalize(z, (float)lv.D));
+    // an axis has a corner in range iff floor in [-1, size-1]; written so that NaN fails
+    const bool ok = (xf >= -1.f) && (xf <= (float)(lv.W - 1)) && (yf >= -1.f) && (yf <= (float)(lv.H - 1)) &&
+                    (zf >= -1.f) && (zf <= (float)(lv.D - 1));
+    if (!ok) return -1;
+    int z0 = (int)zf;
+    z0 = z0 < 0 ? 0 : z0;
+    return z0 / plan.depth;
+}
+
+__device__ __forceinline__ LevelGeom level_geom_of(const Problem &p, int l) {
+    LevelGeom lv;
+    lv.D = (int)p.shapes[3 * l];
+    lv.H = (int)p.shapes[3 * l + 1];
+    lv.W = (int)p.shapes[3 * l + 2];
+    lv.start = (int)p.lsi[l];
+    lv.keep = 0;
+    return lv;
+}
+
+template <typename PT> __device__ __forceinline__ float load1(const PT *p);
+template <> __device__ __forceinline__ float load1<float>(const float *p) { return __ldg(p); }
+template <> __device__ __forceinline__ float load1<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    return __uint_as_float((uint32_t)__ldg(reinterpret_cast<const unsigned short *>(p)) << 16);
+}
+template <> __device__ __forceinline__ float load1<__half>(const __half *p) {
+    return __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(p))));
+}
+template <typename PT> __device__ __forceinline__ void store1(PT *p, float v);
+template <> __device__ __forceinline__ void store1<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void store1<__half>(__half *p, float v) { *p = __float2half_rn(v); }
+
+template <typename PT>
+__global__ void __launch_bounds__(256) fda_bin_count_kernel(const Problem p) {
+    __shared__ BinPlan plan;
+    __shared__ LevelGeom lv;
+    __shared__ unsigned int hist[kMaxSlabs];
+    if (threadIdx.x == 0) {
+        plan = make_bin_plan(p);
+        lv = level_geom_of(p, plan.level);
+    }
+    if (threadIdx.x < kMaxSlabs) hist[threadIdx.x] = 0u;
+    __syncthreads();
+    if (!plan.enabled) return;
+    const int b = blockIdx.y;
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row < p.rows_per_b) {
+        const PT *pr = static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + row) * (size_t)(4 * p.LK) + 3 * plan.level * p.K;
+        for (int k = 0; k < p.K; ++k) {
+            const int sl = slab_of_point(lv, plan, load1<PT>(pr + 3 * k), load1<PT>(pr + 3 * k + 1), load1<PT>(pr + 3 * k + 2));
+            if (sl >= 0) atomicAdd(&hist[sl], 1u);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < plan.slabs && hist[threadIdx.x])
+        atomicAdd(p.bin_counters + (size_t)b * kMaxSlabs + threadIdx.x, hist[threadIdx.x]);
+}
+
+// counters: [0] counts, [1] offsets (exclusive scan per batch element), [2] cursors (zeroed by the host)
+__global__ void fda_bin_scan_kernel(const Problem p) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= p.B) return;
+    const unsigned int *cnt = p.bin_counters + (size_t)b * kMaxSlabs;
+    unsigned int *off = p.bin_counters + (size_t)(p.B + b) * kMaxSlabs;
+    unsigned int run = 0;
+    for (int s = 0; s < kMaxSlabs; ++s) {
+        off[s] = run;
+        run += cnt[s];
+    }
+}
+
+template <typename PT>
+__global__ void __launch_bounds__(256) fda_bin_fill_kernel(const Problem p) {
+    constexpr int kMaxK = 8;
+    __shared__ BinPlan plan;
+    __shared__ LevelGeom lv;
+    __shared__ unsigned int hist[kMaxSlabs];
+    __shared__ unsigned int base[kMaxSlabs];
+    if (threadIdx.x == 0) {
+        plan = make_bin_plan(p);
+        lv = level_geom_of(p, plan.level);
+    }
+    if (threadIdx.x < kMaxSlabs) hist[threadIdx.x] = 0u;
+    __syncthreads();
+    if (!plan.enabled) return;
+    const int b = blockIdx.y;
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    const int LK = p.LK, K = p.K;
+    int slab[kMaxK];
+    unsigned int pos[kMaxK];
+    float prob[kMaxK];
+#pragma unroll
+    for (int k = 0; k < kMaxK; ++k) slab[k] = -1;
+    if (row < p.rows_per_b) {
+        const PT *pr = static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + row) * (size_t)(4 * LK);
+        float m = -INFINITY;
+        for (int j = 0; j < (LK >> 2); ++j) {
+            const float4 lg = load4<PT>(pr + 3 * LK + 4 * j);
+            m = fmaxf(m, fmaxf(fmaxf(lg.x, lg.y), fmaxf(lg.z, lg.w)));
+        }
+        float s = 0.f;
+        for (int j = 0; j < (LK >> 2); ++j) {
+            const float4 lg = load4<PT>(pr + 3 * LK + 4 * j);
+            s += __expf(lg.x - m) + __expf(lg.y - m) + __expf(lg.z - m) + __expf(lg.w - m);
+        }
+        const float inv = 1.0f / s;
+        const PT *pc = pr + 3 * plan.level * K;
+        const PT *pl = pr + 3 * LK + plan.level * K;
+        PT *gr = static_cast<PT *>(p.grad_packed) + ((size_t)b * p.rows_per_b + row) * (size_t)(4 * LK);
+#pragma unroll
+        for (int k = 0; k < kMaxK; ++k) {
+            if (k < K) {
+                slab[k] = slab_of_point(lv, plan, load1<PT>(pc + 3 * k), load1<PT>(pc + 3 * k + 1), load1<PT>(pc + 3 * k + 2));
+                prob[k] = __expf(load1<PT>(pl + k) - m) * inv;
+                if (slab[k] >= 0) {
+                    pos[k] = atomicAdd(&hist[slab[k]], 1u);
+                } else {  // no corner inside the level: the point contributes nothing, its gradients are zero
+                    const int i = plan.level * K + k;
+                    store1<PT>(gr + 3 * i, 0.f); store1<PT>(gr + 3 * i + 1, 0.f); store1<PT>(gr + 3 * i + 2, 0.f);
+                    store1<PT>(gr + 3 * LK + i, 0.f);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < plan.slabs) {
+        const unsigned int n = hist[threadIdx.x];
+        base[threadIdx.x] = n ? atomicAdd(p.bin_counters + (size_t)(2 * p.B + b) * kMaxSlabs + threadIdx.x, n) : 0u;
+    }
+    __syncthreads();
+    if (row < p.rows_per_b) {
+        const unsigned int *off = p.bin_counters + (size_t)(p.B + b) * kMaxSlabs;
+        uint2 *list = p.bin_entries + (size_t)b * p.bin_cap;
+#pragma unroll
+        for (int k = 0; k < kMaxK; ++k) {
+            if (k < K && slab[k] >= 0) {
+                const size_t at = (size_t)off[slab[k]] + base[slab[k]] + pos[k];
+                list[at] = make_uint2((unsigned int)row * (unsigned int)K + (unsigned int)k, __float_as_uint(prob[k]));
+            }
+        }
+    }
+}
+
+template <typename VT, typename PT>
+__global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_binned_kernel(const Problem p) {
+    constexpr int CPL = Vec16<VT>::kCPL;
+    __shared__ BinPlan plan;
+    __shared__ LevelGeom lv_s;
+    if (threadIdx.x == 0) {
+        plan = make_bin_plan(p);
+        lv_s = level_geom_of(p, plan.level);
+    }
+    __syncthreads();
+    const int slab = blockIdx.y, b = blockIdx.z;
+    if (!plan.enabled || slab >= plan.slabs) return;
+    const LevelGeom lv = lv_s;
+    const unsigned int count = p.bin_counters[(size_t)b * kMaxSlabs + slab];
+    const unsigned int offset = p.bin_counters[(size_t)(p.B + b) * kMaxSlabs + slab];
+    const uint2 *list = p.bin_entries + (size_t)b * p.bin_cap + offset;
+
+    const int tid = threadIdx.x;
+    const int gs = 1 << p.gs_log2;
+    const int lane_c = tid & (gs - 1);
+    const int groups_per_block = (int)blockDim.x >> p.gs_log2;
+    const int LK = p.LK, K = p.K;
+#ifndef FDA_BIN_SLAB_POLICY
+#define FDA_BIN_SLAB_POLICY 1
+#endif
+    const uint64_t pol_stream = l2_policy_evict_first();
+    const uint64_t pol_keep = FDA_BIN_SLAB_POLICY == 1 ? l2_policy_evict_last() : l2_policy_evict_normal();
+    const int red_stride = 4 * p.lpg;
+    const int lvl_first = plan.level * K;  // index of the level's first point inside a row
+
+    for (unsigned int e0 = blockIdx.x * groups_per_block; e0 < count; e0 += gridDim.x * groups_per_block) {
+        const unsigned int e = e0 + (tid >> p.gs_log2);
+        const bool have = e < count;
+        uint2 ent = make_uint2(0u, 0u);
+        if (have) ent = __ldcs(list + e);
+        const int row = (int)(ent.x / (unsigned int)K);
+        const int k = (int)(ent.x - (unsigned int)row * (unsigned int)K);
+        const float a = __uint_as_float(ent.y);
+        const bool active = have && lane_c < p.lpg;
+        const size_t grow = (size_t)b * p.rows_per_b + row;
+        const PT *pc = static_cast<const PT *>(p.packed) + grow * (size_t)(4 * LK) + 3 * (lvl_first + k);
+        float x = 0.f, y = 0.f, z = 0.f;
+        if (have) { x = load1<PT>(pc); y = load1<PT>(pc + 1); z = load1<PT>(pc + 2); }
+        const int g = row % p.G;
+        const size_t head_elem = (size_t)b * p.N * p.GD + (size_t)g * p.D + (size_t)lv.start * p.GD;
+        const VT *lvl = static_cast<const VT *>(p.value) + head_elem + (size_t)lane_c * CPL;
+        float *acc_lvl = p.accum + head_elem + (size_t)lane_c * 4;
+        RowGrad<VT> go;
+        go.load(static_cast<const VT *>(p.grad_out) + grow * (size_t)p.D, lane_c, p.lpg, active, pol_stream);
+        float gx, gy, gz, da;
+        point_backward<VT>(lv, p.GD, x, y, z, a, lvl, acc_lvl, go, red_stride, active, gs, pol_keep, pol_keep, gx, gy, gz, da);
+        if (have && lane_c == 0) {
+            PT *gr = static_cast<PT *>(p.grad_packed) + grow * (size_t)(4 * LK);
+            const int i = lvl_first + k;
+            store1<PT>(gr + 3 * i, gx); store1<PT>(gr + 3 * i + 1, gy); store1<PT>(gr + 3 * i + 2, gz);
+            store1<PT>(gr + 3 * LK + i, da);
+        }
+    }
+}
+
+}  // namespace fda

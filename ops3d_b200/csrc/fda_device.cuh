@@ -54,11 +54,46 @@ struct Problem {
     int row_stride;  // floats per staged row in shared memory
     unsigned long long l2_keep_bytes;  // how much per-batch-element data may be marked "evict last" in L2
     int value_elem_bytes;              // sizeof(value dtype)
-    // backward only: the 4-point chunks [chunk_begin, chunk_end) of every row are processed by this launch
-    int chunk_begin, chunk_end;
-    int resume;    // slots of the other chunks are taken from grad_packed (written by an earlier launch)
-    int finalize;  // apply the soft-max backward to the logit slots (last launch over these rows)
+    // backward only
+    int level_mask;  // bit l set: the points of level l are processed by this launch
+    int resume;      // slots of the other levels are taken from grad_packed (written by an earlier launch)
+    int finalize;    // apply the soft-max backward to the logit slots (last launch over these rows)
+    // backward, slab-binned handling of the largest level (see fda_backward_binned.cuh)
+    int bin_allowed;                     // host says scratch is available and the image exceeds the L2 budget
+    unsigned long long bin_slab_bytes;   // target bytes of one slab of the fp32 image
+    unsigned int *bin_counters;          // [3][B][kMaxSlabs]: count, offset, cursor
+    uint2 *bin_entries;                  // [B][bin_cap]: {row * K + k, soft-max probability}
+    unsigned long long bin_cap;          // entries per batch element = rows_per_b * K
 };
+
+constexpr int kMaxSlabs = 64;
+
+// Which level (if any) is handled slab by slab, and how it is cut along z.  A pure function of the
+// shapes and launch parameters, so every kernel of one backward call derives the same plan.
+struct BinPlan {
+    int level, enabled, slabs, depth;
+};
+__device__ __forceinline__ BinPlan make_bin_plan(const Problem &p) {
+    BinPlan plan;
+    plan.level = 0; plan.enabled = 0; plan.slabs = 1; plan.depth = 1;
+    if (!p.bin_allowed) return plan;
+    unsigned long long best = 0;
+    for (int l = 0; l < p.L; ++l) {
+        const unsigned long long c = (unsigned long long)p.shapes[3 * l] * p.shapes[3 * l + 1] * p.shapes[3 * l + 2];
+        if (c > best) { best = c; plan.level = l; }
+    }
+    const unsigned long long image_bytes = best * (unsigned long long)p.GD * 4ull;
+    const int Dz = (int)p.shapes[3 * plan.level];
+    if (!((p.level_mask >> plan.level) & 1) || image_bytes <= p.l2_keep_bytes || Dz < 2) return plan;
+    unsigned long long want = (image_bytes + p.bin_slab_bytes - 1) / p.bin_slab_bytes;
+    if (want > (unsigned long long)kMaxSlabs) want = kMaxSlabs;
+    if (want > (unsigned long long)Dz) want = Dz;
+    if (want < 2) want = 2;
+    plan.depth = (Dz + (int)want - 1) / (int)want;
+    plan.slabs = (Dz + plan.depth - 1) / plan.depth;
+    plan.enabled = 1;
+    return plan;
+}
 
 // ---------------------------------------------------------------------------
 // dtype traits: one 16-byte vector of the value dtype <-> fp32 registers
@@ -192,6 +227,11 @@ __device__ __forceinline__ void red_add_f32x4(float *p, float a, float b, float 
 __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     uint64_t pol;
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
     return pol;
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {

@@ -79,6 +79,7 @@ class PeerReducer:
             raise RuntimeError("FDA_PEER_REDUCE_MODE=multimem but the buffers have no multicast binding")
         self.side = torch.cuda.Stream(device=device, priority=-1)
         self.per_batch = int(self.image[0].numel())
+        self.scratch = None  # slab-binning scratch for one batch element, allocated on first use
         if self.per_batch % 8:
             raise ValueError("elements per batch element must be a multiple of 8")
         # Level schedule: the largest level first (when it sits at either end of the pyramid), so that
@@ -133,14 +134,20 @@ class PeerReducer:
                 self.side.wait_event(done)
                 self._exchange(elem_begin, elem_count, out_elem)
 
+        from . import capi as _capi
+        if self.scratch is None:
+            nbytes = _capi.scratch_bytes(value[:1], packed[:1], K)
+            self.scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=self.device) if nbytes else False
+        scratch = self.scratch if self.scratch is not False else None
+
         def args_of(b):
             return (value[b:b + 1], shapes, lsi, packed[b:b + 1], grad_out[b:b + 1], K, self.image[b:b + 1],
                     grad_packed[b:b + 1])
 
         if self.passes is None:
             for b in range(B):
-                a = args_of(b)
-                capi.backward_accumulate(*a[:7], grad_packed=a[7], im2col_step=im2col_step)
+                capi.backward_accumulate_levels(*args_of(b), 0, shapes.shape[0], capi.BWD_ZERO_IMAGE | capi.BWD_FINALIZE,
+                                                im2col_step=im2col_step, scratch=scratch)
                 hand_over(b * self.per_batch, self.per_batch)
         else:
             # pass-major order: the big level of every batch element first, so that all of its exchanges
@@ -149,7 +156,7 @@ class PeerReducer:
                 last = n == len(self.passes) - 1
                 flags = (capi.BWD_ZERO_IMAGE if n == 0 else capi.BWD_RESUME) | (capi.BWD_FINALIZE if last else 0)
                 for b in range(B):
-                    capi.backward_accumulate_levels(*args_of(b), lb, le, flags, im2col_step=im2col_step)
+                    capi.backward_accumulate_levels(*args_of(b), lb, le, flags, im2col_step=im2col_step, scratch=scratch)
                     hand_over(b * self.per_batch + e0, e1 - e0)
         main.wait_stream(self.side)
         return self.out, grad_packed

@@ -57,8 +57,13 @@ def test_forward_argument_validation_happens_on_the_host():
 
 def test_backward_workspace_contract():
     lib = capi.load()
-    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 0) == 0           # fp32 accumulates in place
-    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 2) == 2 * 100 * 8 * 32 * 4
+    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 50, 4, 0) == 0    # fp32 accumulates in place
+    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 50, 4, 2) == 2 * 100 * 8 * 32 * 4
+    assert lib.fda_backward_scratch_bytes(2, 100, 8, 32, 50, 4) == 0         # image fits L2: no binning
+    # image of one batch element (598016 x 256 x 4 B) exceeds L2: counters + one 8-byte entry per (row, point)
+    big = lib.fda_backward_scratch_bytes(2, 598016, 8, 32, 1000, 8)
+    assert big == 3 * 2 * 64 * 4 + 2 * 1000 * 8 * 8 * 8
+    assert lib.fda_backward_workspace_bytes(2, 598016, 8, 32, 1000, 8, 2) == 2 * 598016 * 256 * 4 + big
     p = ctypes.c_void_p(16)
     args = (1, 8, 1, 8, 1, 1, 4, 2, 0, 64, 1, 0, None)
     assert lib.fda_backward(p, p, p, p, p, p, p, None, 0, *args) == 8        # workspace missing
