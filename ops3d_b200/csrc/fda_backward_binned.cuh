@@ -79,9 +79,14 @@ __global__ void __launch_bounds__(256) fda_bin_count_kernel(const Problem p) {
     const int row = blockIdx.x * blockDim.x + threadIdx.x;
     if (row < p.rows_per_b) {
         const PT *pr = static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + row) * (size_t)(4 * p.LK) + 3 * plan.level * p.K;
-        for (int k = 0; k < p.K; ++k) {
-            const int sl = slab_of_point(lv, plan, load1<PT>(pr + 3 * k), load1<PT>(pr + 3 * k + 1), load1<PT>(pr + 3 * k + 2));
-            if (sl >= 0) atomicAdd(&hist[sl], 1u);
+        for (int j = 0; j < (p.K >> 2); ++j) {  // 4 points = 12 coordinates = three 4-element vectors
+            const float4 c0 = load4<PT>(pr + 12 * j), c1 = load4<PT>(pr + 12 * j + 4), c2 = load4<PT>(pr + 12 * j + 8);
+            const int s0 = slab_of_point(lv, plan, c0.x, c0.y, c0.z), s1 = slab_of_point(lv, plan, c0.w, c1.x, c1.y);
+            const int s2 = slab_of_point(lv, plan, c1.z, c1.w, c2.x), s3 = slab_of_point(lv, plan, c2.y, c2.z, c2.w);
+            if (s0 >= 0) atomicAdd(&hist[s0], 1u);
+            if (s1 >= 0) atomicAdd(&hist[s1], 1u);
+            if (s2 >= 0) atomicAdd(&hist[s2], 1u);
+            if (s3 >= 0) atomicAdd(&hist[s3], 1u);
         }
     }
     __syncthreads();
@@ -140,11 +145,24 @@ __global__ void __launch_bounds__(256) fda_bin_fill_kernel(const Problem p) {
         const PT *pc = pr + 3 * plan.level * K;
         const PT *pl = pr + 3 * LK + plan.level * K;
         PT *gr = static_cast<PT *>(p.grad_packed) + ((size_t)b * p.rows_per_b + row) * (size_t)(4 * LK);
+        float cx[kMaxK], cy[kMaxK], cz[kMaxK], lg[kMaxK];
+#pragma unroll
+        for (int j = 0; j < kMaxK / 4; ++j) {
+            if (4 * j < K) {
+                const float4 c0 = load4<PT>(pc + 12 * j), c1 = load4<PT>(pc + 12 * j + 4), c2 = load4<PT>(pc + 12 * j + 8);
+                const float4 l4 = load4<PT>(pl + 4 * j);
+                cx[4 * j] = c0.x; cy[4 * j] = c0.y; cz[4 * j] = c0.z;
+                cx[4 * j + 1] = c0.w; cy[4 * j + 1] = c1.x; cz[4 * j + 1] = c1.y;
+                cx[4 * j + 2] = c1.z; cy[4 * j + 2] = c1.w; cz[4 * j + 2] = c2.x;
+                cx[4 * j + 3] = c2.y; cy[4 * j + 3] = c2.z; cz[4 * j + 3] = c2.w;
+                lg[4 * j] = l4.x; lg[4 * j + 1] = l4.y; lg[4 * j + 2] = l4.z; lg[4 * j + 3] = l4.w;
+            }
+        }
 #pragma unroll
         for (int k = 0; k < kMaxK; ++k) {
             if (k < K) {
-                slab[k] = slab_of_point(lv, plan, load1<PT>(pc + 3 * k), load1<PT>(pc + 3 * k + 1), load1<PT>(pc + 3 * k + 2));
-                prob[k] = __expf(load1<PT>(pl + k) - m) * inv;
+                slab[k] = slab_of_point(lv, plan, cx[k], cy[k], cz[k]);
+                prob[k] = __expf(lg[k] - m) * inv;
                 if (slab[k] >= 0) {
                     pos[k] = atomicAdd(&hist[slab[k]], 1u);
                 } else {  // no corner inside the level: the point contributes nothing, its gradients are zero
