@@ -248,6 +248,48 @@ def run_reference_arm(args, cfg):
 
 
 # ---------------------------------------------------------------------------------------------
+# optional: the reference's own CUDA kernels on this GPU (reported baseline; needs baseline/_ref/)
+# ---------------------------------------------------------------------------------------------
+def reference_cuda_block(cfg, value, shapes, lsi, packed, grad_out, steps=5, warmup=2):
+    """Times the unmodified reference kernels (built by baseline/build_ref_cuda.sh) on the same inputs.
+    They only take offsets/logits in the value dtype, so ``packed`` is cast to it first."""
+    import importlib.util
+
+    so = os.path.join(ROOT, "baseline", "_ref", "ops3d_ref_C.so")
+    if not os.path.exists(so):
+        return {"unavailable": "baseline/_ref/ops3d_ref_C.so not built (baseline/build_ref_cuda.sh <reference checkout>)"}
+    spec = importlib.util.spec_from_file_location("ops3d_ref_C", so)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    B, Q, G, D, K = cfg["B"], packed.shape[1], cfg["G"], cfg["D"], cfg["K"]
+    pk = packed.to(value.dtype)
+    # launch hints as the reference's findspec / findspec_bwd return them for G*D = 256
+    from ops3d_b200.flash_deform_attn import findspec, findspec_bwd
+    d_f, t_f = findspec(B, Q, G, D)
+    d_b, t_b = findspec_bwd(B, Q, G, D)
+
+    def fwd():
+        return mod.flash_deform_attn_forward(value, shapes, lsi, pk, 64, K, d_f, t_f, True)
+
+    def bwd():
+        return mod.flash_deform_attn_backward(value, shapes, lsi, pk, grad_out, 64, K, d_b, t_b)
+
+    for _ in range(warmup):
+        fwd(); bwd()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    tf = tb = 0.0
+    for _ in range(steps):
+        ev[0].record(); fwd(); ev[1].record(); bwd(); ev[2].record()
+        torch.cuda.synchronize()
+        tf += ev[0].elapsed_time(ev[1]); tb += ev[1].elapsed_time(ev[2])
+    tf /= steps; tb /= steps
+    return {"fwd_ms": tf, "bwd_ms": tb, "value": B / ((tf + tb) * 1e-3), "fwd_value": B / (tf * 1e-3), "unit": "samples/s",
+            "note": "reference csrc/cuda kernels compiled unmodified for sm_100a; offsets/logits cast to the value dtype "
+                    "(the only form they accept); includes their zero-fill and cast passes"}
+
+
+# ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
 def run_ours(args, cfg):
@@ -334,6 +376,10 @@ def run_ours(args, cfg):
     total_ms, fwd_ms, bwd_ms, tail_ms = times.tolist()
     ms_per_step = total_ms / args.steps
 
+    ref_cuda = None
+    if args.ref_cuda and world == 1:
+        ref_cuda = reference_cuda_block(cfg, value, shapes, lsi, packed, grad_out)
+
     # ---- end to end through the public autograd API with host buffers --------------------------------
     e2e_ms, h2d, d2h, e2e_steps = None, 0, 0, 0
     if not args.no_e2e:
@@ -416,6 +462,8 @@ def run_ours(args, cfg):
                                           else (3 if vdt != torch.float32 else 2)),
             "clocks": clocks,
         }
+        if ref_cuda is not None:
+            line["reference_cuda"] = ref_cuda
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_block(cfg)
         print(json.dumps(line), flush=True)
@@ -436,6 +484,8 @@ def main():
                     help="N > 1: how the fp32 grad_value images are summed (fused peer-memory kernel, or NCCL all-reduce + cast)")
     ap.add_argument("--batch", type=int, default=0, help="override B (smaller case for profiler captures)")
     ap.add_argument("--queries", type=int, default=0, help="override Lq (smaller case for profiler captures)")
+    ap.add_argument("--ref-cuda", action="store_true",
+                    help="also time the reference's own CUDA kernels (needs baseline/_ref/ops3d_ref_C.so; N=1)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
