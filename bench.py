@@ -55,6 +55,11 @@ CONFIGS = {
 }
 METRIC = "fwd+bwd samples/s (fwd samples/s and achieved GB/s vs HBM roofline beside it)"
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per full-size launch of the backward kernels of
+# config 5, from the ncu captures summarised under profiles/: measured on the reduced case
+# (--batch 1 --queries 74752, 1/16 of the rows over the same per-batch-element volume) and scaled x16.
+NCU_BACKWARD_TRAFFIC_BYTES = {5: 16 * (3.36e9 + 3.10e9)}
+
 
 # ---------------------------------------------------------------------------------------------
 # synthetic inputs
@@ -431,8 +436,11 @@ def run_ours(args, cfg):
         peak, peak_src = 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
     achieved = bm["bwd_kernel"] / (bwd_ms * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "fda_backward_kernel (timed with its zero-fill of the fp32 image)",
-        "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+        "bound": "hbm",
+        "kernel": "backward pass = zero-fill + slab binning + fda_backward_binned_kernel + fda_backward_kernel (one C-ABI call)",
+        "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+        "traffic": (NCU_BACKWARD_TRAFFIC_BYTES.get(args.config) if (world == 1 and not args.batch and not args.queries) else None),
+        "traffic_source": "ncu capture of a 1/16-row case scaled x16 (profiles/), both backward kernels",
         "peak_source": peak_src, "algorithmic_bytes_per_launch": bm["bwd_kernel"], "ms_per_launch": bwd_ms,
         "fwd_kernel": {"achieved": bm["fwd"] / (fwd_ms * 1e-3) / 1e9, "frac": bm["fwd"] / (fwd_ms * 1e-3) / 1e9 / peak,
                        "algorithmic_bytes_per_launch": bm["fwd"], "ms_per_launch": fwd_ms},
