@@ -187,6 +187,21 @@ int fda_peer_reduce_cast(const float *const *peer_images, void *const *peer_outp
                          size_t num_elements, int value_dtype, void *stream);
 
 /*
+ * Push variant of the same exchange, in two calls with a cross-rank barrier between them (and the
+ * usual one after): fda_peer_push_partials stores the slices of the local image that other ranks
+ * own into their staging areas (peer_staging: HOST array of `world` DEVICE pointers, each area
+ * world * slot_stride_elements floats; this rank writes slot `rank` of every other area), then
+ * fda_peer_reduce_staged_cast sums the own slice of the local image with the world-1 partials staged
+ * locally, converts, and stores the result into every rank's grad_value.  slot_stride_elements is a
+ * multiple of 8 and at least the longest slice.  No counterpart in the reference.
+ */
+int fda_peer_push_partials(const float *image, float *const *peer_staging, size_t slot_stride_elements,
+                           int world, int rank, size_t num_elements, void *stream);
+int fda_peer_reduce_staged_cast(const float *image, const float *staging, size_t slot_stride_elements,
+                                void *const *peer_outputs, int world, int rank, size_t num_elements,
+                                int value_dtype, void *stream);
+
+/*
  * Same exchange through NVSwitch multicast (NVLS): mc_image and mc_output are the MULTICAST
  * addresses of the fp32 image and of grad_value (both bound on all `world` ranks).  This rank's
  * slice is summed in the switch (multimem.ld_reduce .add.f32), converted once, and written to

@@ -18,6 +18,7 @@ EXPORTS = (
     "fda_status_string", "fda_last_cuda_error", "fda_version", "fda_forward",
     "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
+    "fda_peer_push_partials", "fda_peer_reduce_staged_cast",
 )
 BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE = 1, 2, 4
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
@@ -62,6 +63,10 @@ def load() -> ctypes.CDLL:
     lib.fda_backward_noalloc.restype = i
     lib.fda_peer_reduce_cast.argtypes = [vp, vp, i, i, sz, i, vp]
     lib.fda_peer_reduce_cast.restype = i
+    lib.fda_peer_push_partials.argtypes = [vp, vp, sz, i, i, sz, vp]
+    lib.fda_peer_push_partials.restype = i
+    lib.fda_peer_reduce_staged_cast.argtypes = [vp, vp, sz, vp, i, i, sz, i, vp]
+    lib.fda_peer_reduce_staged_cast.restype = i
     lib.fda_multimem_reduce_cast.argtypes = [vp, vp, i, i, sz, i, vp]
     lib.fda_multimem_reduce_cast.restype = i
     _lib = lib
@@ -197,3 +202,21 @@ def multimem_reduce_cast(mc_image_ptr, mc_output_ptr, world, rank, num_elements,
     with torch.cuda.device(device):
         check(load().fda_multimem_reduce_cast(mc_image_ptr + byte_offsets[0], mc_output_ptr + byte_offsets[1], world, rank,
                                               num_elements, DTYPE_CODE[dtype], torch.cuda.current_stream(device).cuda_stream))
+
+
+def peer_push_partials(image_ptr, staging_ptrs, slot_stride, rank, num_elements, device):
+    """``fda_peer_push_partials``: ``image_ptr`` = local image (int address, already offset to the range),
+    ``staging_ptrs`` = per-rank staging addresses."""
+    world = len(staging_ptrs)
+    st = (ctypes.c_void_p * world)(*staging_ptrs)
+    with torch.cuda.device(device):
+        check(load().fda_peer_push_partials(image_ptr, st, slot_stride, world, rank, num_elements,
+                                            torch.cuda.current_stream(device).cuda_stream))
+
+
+def peer_reduce_staged_cast(image_ptr, staging_ptr, slot_stride, output_ptrs, rank, num_elements, dtype, device):
+    world = len(output_ptrs)
+    outs = (ctypes.c_void_p * world)(*output_ptrs)
+    with torch.cuda.device(device):
+        check(load().fda_peer_reduce_staged_cast(image_ptr, staging_ptr, slot_stride, outs, world, rank, num_elements,
+                                                 DTYPE_CODE[dtype], torch.cuda.current_stream(device).cuda_stream))

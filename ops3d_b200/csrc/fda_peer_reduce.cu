@@ -168,6 +168,70 @@ __global__ void __launch_bounds__(512) fda_multimem_reduce_cast_kernel(const flo
     }
 }
 
+// Push variant of the exchange (posted peer stores instead of peer loads): every rank first writes
+// the slices it does NOT own into the owners' staging areas, then -- after a barrier -- each owner
+// sums its own slice of its image with the world-1 staged partials, converts, and pushes the
+// result to every rank.  NVLink carries writes at a higher rate than SM-issued reads.
+struct PushPtrs {
+    float *staging[kMaxPeers];  // position p = staging area of rank (rank + p) % world
+    size_t slice_begin[kMaxPeers], slice_end[kMaxPeers];  // that rank's slice, in 8-element units
+};
+
+template <int UNROLL>
+__global__ void __launch_bounds__(512) fda_peer_push_kernel(const float *__restrict__ image, const PushPtrs pp, const int world,
+                                                            const size_t my_slot_offset /* floats */) {
+    // blockIdx.y = peer position 1..world-1; x strides over that peer's slice
+    const int p = blockIdx.y + 1;
+    if (p >= world) return;
+    const size_t ub = pp.slice_begin[p], ue = pp.slice_end[p];
+    float *dst = pp.staging[p] + my_slot_offset;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t u0 = ub + (size_t)blockIdx.x * blockDim.x + threadIdx.x; u0 < ue; u0 += stride * UNROLL) {
+        float4 lo[UNROLL], hi[UNROLL];
+#pragma unroll
+        for (int j = 0; j < UNROLL; ++j) {
+            const size_t u = u0 + (size_t)j * stride;
+            if (u < ue) {
+                const float4 *src = reinterpret_cast<const float4 *>(image + u * 8);
+                lo[j] = __ldcs(src);
+                hi[j] = __ldcs(src + 1);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < UNROLL; ++j) {
+            const size_t u = u0 + (size_t)j * stride;
+            if (u < ue) {
+                float4 *d = reinterpret_cast<float4 *>(dst + (u - ub) * 8);
+                d[0] = lo[j];
+                d[1] = hi[j];
+            }
+        }
+    }
+}
+
+// Owner side: image slice + staged partials (fixed order: own image, then slots 0..world-1 skipping
+// the own one) -> value dtype -> every rank's grad_value.
+template <typename VT, int UNROLL>
+__global__ void __launch_bounds__(512) fda_peer_reduce_staged_kernel(const float *__restrict__ image,
+                                                                     const float *__restrict__ staging, size_t slot_stride,
+                                                                     const PeerPtrs pp, const int world, const int rank,
+                                                                     size_t unit_begin, size_t unit_end) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t u = unit_begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < unit_end; u += stride) {
+        const float4 *src = reinterpret_cast<const float4 *>(image + u * 8);
+        float4 l = __ldcs(src), h = __ldcs(src + 1);
+        float a[8] = {l.x, l.y, l.z, l.w, h.x, h.y, h.z, h.w};
+        for (int s = 0; s < world; ++s) {
+            if (s == rank) continue;
+            const float4 *q = reinterpret_cast<const float4 *>(staging + (size_t)s * slot_stride + (u - unit_begin) * 8);
+            l = __ldcg(q); h = __ldcg(q + 1);  // written by a peer: read at L2
+            a[0] += l.x; a[1] += l.y; a[2] += l.z; a[3] += l.w;
+            a[4] += h.x; a[5] += h.y; a[6] += h.z; a[7] += h.w;
+        }
+        for (int p = 0; p < world; ++p) Out8<VT>::store(pp.out[p], u, a);
+    }
+}
+
 int env_int(const char *name, int dflt) {
     const char *e = std::getenv(name);
     return e ? std::atoi(e) : dflt;
@@ -177,8 +241,9 @@ template <typename VT>
 cudaError_t launch(const PeerPtrs &pp, int world, size_t ub, size_t ue, cudaStream_t st) {
     const size_t units = ue - ub;
     if (units == 0) return cudaSuccess;
-    // Few, fat blocks: the kernel is bound by NVLink, not by SM throughput (FDA_PEER_REDUCE_BLOCKS overrides).
-    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 64);
+    // Few, fat blocks: the kernel is bound by NVLink, not by SM throughput -- measured time is the same from 16
+    // to 1184 blocks, and fewer blocks slow the overlapped scatter kernel less (FDA_PEER_REDUCE_BLOCKS overrides).
+    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 16);
     if (max_blocks < 1) max_blocks = 1;
     const int threads = 512;
     size_t blocks = (units + threads - 1) / threads;
@@ -197,7 +262,7 @@ template <typename VT>
 cudaError_t launch_multimem(const float *mc_image, void *mc_out, size_t ub, size_t ue, cudaStream_t st) {
     const size_t units = ue - ub;
     if (units == 0) return cudaSuccess;
-    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 64);
+    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 16);
     if (max_blocks < 1) max_blocks = 1;
     const int threads = 512;
     size_t blocks = (units + threads - 1) / threads;
@@ -223,6 +288,74 @@ extern "C" int fda_multimem_reduce_cast(const float *mc_image, void *mc_output, 
     else if (value_dtype == FDA_DTYPE_F16) e = launch_multimem<__half>(mc_image, mc_output, ub, ue, st);
     else e = launch_multimem<__nv_bfloat16>(mc_image, mc_output, ub, ue, st);
     return e == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
+}
+
+extern "C" int fda_peer_push_partials(const float *image, float *const *peer_staging, size_t slot_stride_elements,
+                                      int world, int rank, size_t num_elements, void *stream) {
+    if (!image || !peer_staging) return FDA_ERR_NULL_POINTER;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return FDA_ERR_BAD_SHAPE;
+    if (num_elements % 8 != 0 || slot_stride_elements % 8 != 0) return FDA_ERR_BAD_SHAPE;
+    if (world == 1) return FDA_OK;
+    const size_t units = num_elements / 8;
+    PushPtrs pp;
+    size_t longest = 0;
+    for (int p = 0; p < kMaxPeers; ++p) { pp.staging[p] = nullptr; pp.slice_begin[p] = pp.slice_end[p] = 0; }
+    for (int p = 0; p < world; ++p) {
+        const int r = (rank + p) % world;
+        if (!peer_staging[r]) return FDA_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(peer_staging[r]) & 15u) return FDA_ERR_MISALIGNED;
+        pp.staging[p] = peer_staging[r];
+        pp.slice_begin[p] = units * (size_t)r / world;
+        pp.slice_end[p] = units * (size_t)(r + 1) / world;
+        const size_t len = pp.slice_end[p] - pp.slice_begin[p];
+        if (len * 8 > slot_stride_elements) return FDA_ERR_BAD_SHAPE;
+        if (len > longest) longest = len;
+    }
+    if (longest == 0) return FDA_OK;
+    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 16);
+    if (max_blocks < 1) max_blocks = 1;
+    int bx = max_blocks / (world - 1);
+    if (bx < 1) bx = 1;
+    const size_t want = (longest + 511) / 512;
+    if ((size_t)bx > want) bx = (int)want;
+    const dim3 grid((unsigned)bx, (unsigned)(world - 1), 1);
+    fda_peer_push_kernel<4><<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(image, pp, world,
+                                                                                (size_t)rank * slot_stride_elements);
+    return cudaGetLastError() == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
+}
+
+extern "C" int fda_peer_reduce_staged_cast(const float *image, const float *staging, size_t slot_stride_elements,
+                                           void *const *peer_outputs, int world, int rank, size_t num_elements,
+                                           int value_dtype, void *stream) {
+    if (!image || !staging || !peer_outputs) return FDA_ERR_NULL_POINTER;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return FDA_ERR_BAD_SHAPE;
+    if (value_dtype < 0 || value_dtype > 2) return FDA_ERR_BAD_DTYPE;
+    if (num_elements % 8 != 0 || slot_stride_elements % 8 != 0) return FDA_ERR_BAD_SHAPE;
+    PeerPtrs pp;
+    for (int p = 0; p < kMaxPeers; ++p) { pp.img[p] = nullptr; pp.out[p] = nullptr; }
+    for (int p = 0; p < world; ++p) {
+        const int r = (rank + p) % world;
+        if (!peer_outputs[r]) return FDA_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(peer_outputs[r]) & 15u) return FDA_ERR_MISALIGNED;
+        pp.out[p] = peer_outputs[r];
+    }
+    const size_t units = num_elements / 8;
+    const size_t ub = units * (size_t)rank / world, ue = units * (size_t)(rank + 1) / world;
+    if (ue == ub) return FDA_OK;
+    if ((ue - ub) * 8 > slot_stride_elements) return FDA_ERR_BAD_SHAPE;
+    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 16);
+    if (max_blocks < 1) max_blocks = 1;
+    size_t blocks = (ue - ub + 511) / 512;
+    if (blocks > (size_t)max_blocks) blocks = (size_t)max_blocks;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned g = (unsigned)blocks;
+    if (value_dtype == FDA_DTYPE_F32)
+        fda_peer_reduce_staged_kernel<float, 1><<<g, 512, 0, st>>>(image, staging, slot_stride_elements, pp, world, rank, ub, ue);
+    else if (value_dtype == FDA_DTYPE_F16)
+        fda_peer_reduce_staged_kernel<__half, 1><<<g, 512, 0, st>>>(image, staging, slot_stride_elements, pp, world, rank, ub, ue);
+    else
+        fda_peer_reduce_staged_kernel<__nv_bfloat16, 1><<<g, 512, 0, st>>>(image, staging, slot_stride_elements, pp, world, rank, ub, ue);
+    return cudaGetLastError() == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
 }
 
 extern "C" int fda_peer_reduce_cast(const float *const *peer_images, void *const *peer_outputs, int world, int rank,

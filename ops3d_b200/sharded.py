@@ -71,7 +71,7 @@ class PeerReducer:
         self.out_ptrs = [int(p) for p in self.h_out.buffer_ptrs]
         self.mc_image = int(getattr(self.h_image, "multicast_ptr", 0) or 0)
         self.mc_out = int(getattr(self.h_out, "multicast_ptr", 0) or 0)
-        mode = os.environ.get("FDA_PEER_REDUCE_MODE", "auto")  # auto | multimem | p2p
+        mode = os.environ.get("FDA_PEER_REDUCE_MODE", "auto")  # auto | multimem | p2p (pull) | push
         # Measured on 8 x B200: standing alone the in-switch reduction is the faster exchange (3.7 vs 4.4 ms
         # for a 1.22 GB image), but overlapped with the slab-binned backward it is the slower one (step
         # 10.0 vs 8.4 ms): plain peer loads disturb the L2-resident slabs less.  So peer loads by default.
@@ -81,6 +81,13 @@ class PeerReducer:
             raise RuntimeError("FDA_PEER_REDUCE_MODE=multimem but the buffers have no multicast binding")
         self.side = torch.cuda.Stream(device=device, priority=-1)
         self.per_batch = int(self.image[0].numel())
+        self.use_push = mode == "push" and self.world > 1
+        if self.use_push:
+            # staging: one slot per source rank, each as long as the longest slice of the largest exchange
+            self.slot = ((self.per_batch // 8 + self.world - 1) // self.world) * 8
+            self.staging = symm_mem.empty(self.world * self.slot, dtype=torch.float32, device=device)
+            self.h_staging = symm_mem.rendezvous(self.staging, self.group)
+            self.staging_ptrs = [int(p) for p in self.h_staging.buffer_ptrs]
         self.scratch = None  # slab-binning scratch for one batch element, allocated on first use
         if self.per_batch % 8:
             raise ValueError("elements per batch element must be a multiple of 8")
@@ -108,6 +115,14 @@ class PeerReducer:
         from . import capi
 
         offs = (elem_begin * 4, elem_begin * out_elem)
+        if self.use_push:
+            img = self.image_ptrs[self.rank] + offs[0]
+            capi.peer_push_partials(img, self.staging_ptrs, self.slot, self.rank, elem_count, self.device)
+            self.h_image.barrier(channel=0)   # every rank's partials have landed in the owners' staging areas
+            capi.peer_reduce_staged_cast(img, self.staging_ptrs[self.rank], self.slot,
+                                         [p + offs[1] for p in self.out_ptrs], self.rank, elem_count, self.dtype, self.device)
+            self.h_out.barrier(channel=0)     # every rank's results have landed; staging areas are free again
+            return
         self.h_image.barrier(channel=0)   # every rank's part of the image is complete
         if self.use_multimem:             # in-switch sum (NVLS): 1/R of the bytes per GPU
             capi.multimem_reduce_cast(self.mc_image, self.mc_out, self.world, self.rank, elem_count, self.dtype,

@@ -32,7 +32,9 @@ def _free_port():
 
 
 def _worker(rank, world, port, mode, ret):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", FDA_SHARDED_REDUCE=mode)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      FDA_SHARDED_REDUCE="nccl" if mode == "nccl" else "peer",
+                      FDA_PEER_REDUCE_MODE="auto" if mode == "nccl" else mode)
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -64,7 +66,7 @@ def _worker(rank, world, port, mode, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["peer", "nccl"])
+@pytest.mark.parametrize("mode", ["p2p", "push", "multimem", "nccl"])
 def test_two_gpus_sharded_equals_unsharded(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
