@@ -85,10 +85,17 @@ __device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, floa
         }
         float v[CPL];
         Vec16<VT>::unpack(raw[n], v);
+#ifdef FDA_NO_FFMA2
         float d = 0.f;
 #pragma unroll
         for (int k = 0; k < CPL; ++k) d = fmaf(v[k], go.d[k], d);
         dot[n] = d;  // 0 for corners outside the level
+#else
+        float d0 = 0.f, d1 = 0.f;  // even / odd channels, two per instruction
+#pragma unroll
+        for (int k = 0; k < CPL; k += 2) ffma2(d0, d1, v[k], v[k + 1], go.d[k], go.d[k + 1]);
+        dot[n] = d0 + d1;  // 0 for corners outside the level
+#endif
     }
     // d out / d x_im = sum_{z,y} wz*wy*(dot[z,y,1] - dot[z,y,0]), likewise y and z; dalpha = sum w*dot
     const float wzy[4] = {pg.wz[0] * pg.wy[0], pg.wz[0] * pg.wy[1], pg.wz[1] * pg.wy[0], pg.wz[1] * pg.wy[1]};

@@ -222,19 +222,34 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
     const int red_stride = 4 * p.lpg;
     const int lvl_first = plan.level * K;  // index of the level's first point inside a row
 
-    for (unsigned int e0 = blockIdx.x * groups_per_block; e0 < count; e0 += gridDim.x * groups_per_block) {
-        const unsigned int e = e0 + (tid >> p.gs_log2);
+    // Software pipeline over this group's entries: the entry is fetched two iterations ahead and its
+    // coordinates one iteration ahead, so that the dependent chain entry -> coordinates -> corner
+    // gathers costs one memory latency per iteration instead of three.
+    const unsigned int step = gridDim.x * groups_per_block;
+    const unsigned int first = blockIdx.x * groups_per_block + (tid >> p.gs_log2);
+    const PT *packed_b = static_cast<const PT *>(p.packed) + (size_t)b * p.rows_per_b * (size_t)(4 * LK) + 3 * lvl_first;
+    auto fetch_entry = [&](unsigned int e) -> uint2 { return e < count ? __ldcs(list + e) : make_uint2(0u, 0u); };
+    auto fetch_coords = [&](const uint2 &ent, bool have, float &x, float &y, float &z) {
+        x = y = z = 0.f;
+        if (have) {
+            const unsigned int row = ent.x / (unsigned int)K, k = ent.x - row * (unsigned int)K;
+            const PT *pc = packed_b + (size_t)row * (size_t)(4 * LK) + 3 * k;
+            x = load1<PT>(pc); y = load1<PT>(pc + 1); z = load1<PT>(pc + 2);
+        }
+    };
+    uint2 ent_cur = fetch_entry(first), ent_nxt = fetch_entry(first + step);
+    float x, y, z;
+    fetch_coords(ent_cur, first < count, x, y, z);
+    for (unsigned int e = first, base = blockIdx.x * groups_per_block; base < count; base += step, e += step) {
+        const uint2 ent_nn = fetch_entry(e + 2 * step);
+        float xn, yn, zn;
+        fetch_coords(ent_nxt, e + step < count, xn, yn, zn);
         const bool have = e < count;
-        uint2 ent = make_uint2(0u, 0u);
-        if (have) ent = __ldcs(list + e);
-        const int row = (int)(ent.x / (unsigned int)K);
-        const int k = (int)(ent.x - (unsigned int)row * (unsigned int)K);
-        const float a = __uint_as_float(ent.y);
+        const int row = (int)(ent_cur.x / (unsigned int)K);
+        const int k = (int)(ent_cur.x - (unsigned int)row * (unsigned int)K);
+        const float a = __uint_as_float(ent_cur.y);
         const bool active = have && lane_c < p.lpg;
         const size_t grow = (size_t)b * p.rows_per_b + row;
-        const PT *pc = static_cast<const PT *>(p.packed) + grow * (size_t)(4 * LK) + 3 * (lvl_first + k);
-        float x = 0.f, y = 0.f, z = 0.f;
-        if (have) { x = load1<PT>(pc); y = load1<PT>(pc + 1); z = load1<PT>(pc + 2); }
         const int g = row % p.G;
         const size_t head_elem = (size_t)b * p.N * p.GD + (size_t)g * p.D + (size_t)lv.start * p.GD;
         const VT *lvl = static_cast<const VT *>(p.value) + head_elem + (size_t)lane_c * CPL;
@@ -249,6 +264,8 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
             store1<PT>(gr + 3 * i, gx); store1<PT>(gr + 3 * i + 1, gy); store1<PT>(gr + 3 * i + 2, gz);
             store1<PT>(gr + 3 * LK + i, da);
         }
+        ent_cur = ent_nxt; ent_nxt = ent_nn;
+        x = xn; y = yn; z = zn;
     }
 }
 

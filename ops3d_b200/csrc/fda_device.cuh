@@ -154,6 +154,30 @@ template <> struct Vec16<__half> {
     }
 };
 
+// Packed fp32 x2 fused multiply-add (sm_100: one instruction for two lanes of fp32, same rounding as fmaf).
+__device__ __forceinline__ void ffma2(float &d0, float &d1, float a0, float a1, float b0, float b1) {
+    unsigned long long ra, rb, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b0), "f"(b1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rd) : "f"(d0), "f"(d1));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(rd) : "l"(ra), "l"(rb));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(rd));
+}
+
+// acc[k] += w * v[k] for one 16-byte vector of the value dtype, two channels per instruction
+template <typename VT>
+__device__ __forceinline__ void axpy16(const uint4 &raw, float w, float (&acc)[Vec16<VT>::kCPL]) {
+    float v[Vec16<VT>::kCPL];
+    Vec16<VT>::unpack(raw, v);
+#ifdef FDA_NO_FFMA2
+#pragma unroll
+    for (int k = 0; k < Vec16<VT>::kCPL; ++k) acc[k] = fmaf(w, v[k], acc[k]);
+#else
+#pragma unroll
+    for (int k = 0; k < Vec16<VT>::kCPL; k += 2) ffma2(acc[k], acc[k + 1], w, w, v[k], v[k + 1]);
+#endif
+}
+
 // Four consecutive elements (aligned to four elements) <-> float4.
 template <typename T> __device__ __forceinline__ float4 load4(const T *p);
 template <> __device__ __forceinline__ float4 load4<float>(const float *p) {

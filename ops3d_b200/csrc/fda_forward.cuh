@@ -109,10 +109,7 @@ __global__ void __launch_bounds__(kThreads, FDA_FWD_MIN_BLOCKS) fda_forward_kern
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 const float w = a * ((pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2]);
-                float v[CPL];
-                Vec16<VT>::unpack(raw[n], v);
-#pragma unroll
-                for (int k = 0; k < CPL; ++k) acc[k] = fmaf(w, v[k], acc[k]);
+                axpy16<VT>(raw[n], w, acc);
             }
         }
     }
