@@ -178,7 +178,15 @@ int launch_binned(fda::Problem p, cudaStream_t st) {
     const dim3 rows_grid((unsigned)((p.rows_per_b + 255) / 256), (unsigned)p.B, 1);
     fda::fda_bin_count_kernel<PT><<<rows_grid, 256, 0, st>>>(p);
     fda::fda_bin_scan_kernel<<<(unsigned)((p.B + 127) / 128), 128, 0, st>>>(p);
-    fda::fda_bin_fill_kernel<PT><<<rows_grid, 256, 0, st>>>(p);
+    {
+        fda::Problem q = p;
+        q.row_stride = padded_stride(4 * p.LK);
+        const int threads = pick_threads(q, q.row_stride);
+        const size_t smem = (size_t)(threads >> q.gs_log2) * q.row_stride * sizeof(float);
+        auto kern = fda::fda_bin_fill_kernel<PT>;
+        if (int rc = ensure_smem(reinterpret_cast<const void *>(kern), smem)) return rc;
+        kern<<<row_grid(q, threads), threads, smem, st>>>(q);
+    }
     // x: blocks striding over one slab's list; y: slab (slabs run one after the other); z: batch element
     const dim3 grid(592, fda::kMaxSlabs, (unsigned)p.B);
     fda::fda_backward_binned_kernel<VT, PT><<<grid, fda::kThreads, 0, st>>>(p);

@@ -10,7 +10,8 @@
 //   fda_bin_count_kernel   one thread per row: which slab does each of the level's K points fall in;
 //                          block histogram in shared memory, one global atomic per slab and block
 //   fda_bin_scan_kernel    exclusive scan of the slab counts of every batch element
-//   fda_bin_fill_kernel    one thread per row: soft-max of the row, then appends {row*K+k, probability}
+//   fda_bin_fill_kernel    one lane group per row (rows staged like in fda_backward_kernel): soft-max of
+//                          the row, then appends {row*K+k, probability}
 //                          to the point's slab list (block-local positions from shared-memory atomics,
 //                          one global reservation per slab and block); points with no corner inside the
 //                          level get their zero gradients written here
@@ -107,66 +108,70 @@ __global__ void fda_bin_scan_kernel(const Problem p) {
     }
 }
 
+// Same row -> lane-group mapping and warp-private staging as fda_backward_kernel, so the packed rows are
+// read with coalesced vector loads; the K points of the level are spread over the lanes of the row.
 template <typename PT>
-__global__ void __launch_bounds__(256) fda_bin_fill_kernel(const Problem p) {
+__global__ void __launch_bounds__(kThreads) fda_bin_fill_kernel(const Problem p) {
     constexpr int kMaxK = 8;
     __shared__ BinPlan plan;
     __shared__ LevelGeom lv;
     __shared__ unsigned int hist[kMaxSlabs];
     __shared__ unsigned int base[kMaxSlabs];
-    if (threadIdx.x == 0) {
+    extern __shared__ __align__(16) float smem_tile[];
+    const int tid = threadIdx.x;
+    if (tid == 0) {
         plan = make_bin_plan(p);
         lv = level_geom_of(p, plan.level);
     }
-    if (threadIdx.x < kMaxSlabs) hist[threadIdx.x] = 0u;
+    if (tid < kMaxSlabs) hist[tid] = 0u;
     __syncthreads();
     if (!plan.enabled) return;
     const int b = blockIdx.y;
-    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    const int gs = 1 << p.gs_log2;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int lane_c = tid & (gs - 1);
+    const int rows_per_block = (int)blockDim.x >> p.gs_log2;
+    const int rows_per_warp = 32 >> p.gs_log2;
+    const int row = blockIdx.x * rows_per_block + (tid >> p.gs_log2);
+    const bool row_ok = row < p.rows_per_b;
     const int LK = p.LK, K = p.K;
+    const int first = blockIdx.x * rows_per_block + warp * rows_per_warp;
+    float *wtile = smem_tile + warp * rows_per_warp * p.row_stride;
+    int nrows = p.rows_per_b - first;
+    nrows = nrows < 0 ? 0 : (nrows > rows_per_warp ? rows_per_warp : nrows);
+    stage_rows<PT>(static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + first) * (size_t)(4 * LK), wtile, nrows,
+                   LK, p.row_stride, lane);
+    __syncwarp();
+    const float *trow = wtile + (lane >> p.gs_log2) * p.row_stride;
+
     int slab[kMaxK];
     unsigned int pos[kMaxK];
     float prob[kMaxK];
 #pragma unroll
-    for (int k = 0; k < kMaxK; ++k) slab[k] = -1;
-    if (row < p.rows_per_b) {
-        const PT *pr = static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + row) * (size_t)(4 * LK);
+    for (int j = 0; j < kMaxK; ++j) slab[j] = -2;  // -2: no point for this lane, -1: point without a corner in range
+    if (row_ok) {
         float m = -INFINITY;
         for (int j = 0; j < (LK >> 2); ++j) {
-            const float4 lg = load4<PT>(pr + 3 * LK + 4 * j);
+            const float4 lg = *reinterpret_cast<const float4 *>(trow + 3 * LK + 4 * j);
             m = fmaxf(m, fmaxf(fmaxf(lg.x, lg.y), fmaxf(lg.z, lg.w)));
         }
         float s = 0.f;
         for (int j = 0; j < (LK >> 2); ++j) {
-            const float4 lg = load4<PT>(pr + 3 * LK + 4 * j);
+            const float4 lg = *reinterpret_cast<const float4 *>(trow + 3 * LK + 4 * j);
             s += __expf(lg.x - m) + __expf(lg.y - m) + __expf(lg.z - m) + __expf(lg.w - m);
         }
         const float inv = 1.0f / s;
-        const PT *pc = pr + 3 * plan.level * K;
-        const PT *pl = pr + 3 * LK + plan.level * K;
         PT *gr = static_cast<PT *>(p.grad_packed) + ((size_t)b * p.rows_per_b + row) * (size_t)(4 * LK);
-        float cx[kMaxK], cy[kMaxK], cz[kMaxK], lg[kMaxK];
 #pragma unroll
-        for (int j = 0; j < kMaxK / 4; ++j) {
-            if (4 * j < K) {
-                const float4 c0 = load4<PT>(pc + 12 * j), c1 = load4<PT>(pc + 12 * j + 4), c2 = load4<PT>(pc + 12 * j + 8);
-                const float4 l4 = load4<PT>(pl + 4 * j);
-                cx[4 * j] = c0.x; cy[4 * j] = c0.y; cz[4 * j] = c0.z;
-                cx[4 * j + 1] = c0.w; cy[4 * j + 1] = c1.x; cz[4 * j + 1] = c1.y;
-                cx[4 * j + 2] = c1.z; cy[4 * j + 2] = c1.w; cz[4 * j + 2] = c2.x;
-                cx[4 * j + 3] = c2.y; cy[4 * j + 3] = c2.z; cz[4 * j + 3] = c2.w;
-                lg[4 * j] = l4.x; lg[4 * j + 1] = l4.y; lg[4 * j + 2] = l4.z; lg[4 * j + 3] = l4.w;
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < kMaxK; ++k) {
+        for (int j = 0; j < kMaxK; ++j) {
+            const int k = lane_c + j * gs;
             if (k < K) {
-                slab[k] = slab_of_point(lv, plan, cx[k], cy[k], cz[k]);
-                prob[k] = __expf(lg[k] - m) * inv;
-                if (slab[k] >= 0) {
-                    pos[k] = atomicAdd(&hist[slab[k]], 1u);
+                const int i = plan.level * K + k;
+                slab[j] = slab_of_point(lv, plan, trow[3 * i], trow[3 * i + 1], trow[3 * i + 2]);
+                prob[j] = __expf(trow[3 * LK + i] - m) * inv;
+                if (slab[j] >= 0) {
+                    pos[j] = atomicAdd(&hist[slab[j]], 1u);
                 } else {  // no corner inside the level: the point contributes nothing, its gradients are zero
-                    const int i = plan.level * K + k;
                     store1<PT>(gr + 3 * i, 0.f); store1<PT>(gr + 3 * i + 1, 0.f); store1<PT>(gr + 3 * i + 2, 0.f);
                     store1<PT>(gr + 3 * LK + i, 0.f);
                 }
@@ -174,19 +179,20 @@ __global__ void __launch_bounds__(256) fda_bin_fill_kernel(const Problem p) {
         }
     }
     __syncthreads();
-    if (threadIdx.x < plan.slabs) {
-        const unsigned int n = hist[threadIdx.x];
-        base[threadIdx.x] = n ? atomicAdd(p.bin_counters + (size_t)(2 * p.B + b) * kMaxSlabs + threadIdx.x, n) : 0u;
+    if (tid < plan.slabs) {
+        const unsigned int n = hist[tid];
+        base[tid] = n ? atomicAdd(p.bin_counters + (size_t)(2 * p.B + b) * kMaxSlabs + tid, n) : 0u;
     }
     __syncthreads();
-    if (row < p.rows_per_b) {
+    if (row_ok) {
         const unsigned int *off = p.bin_counters + (size_t)(p.B + b) * kMaxSlabs;
         uint2 *list = p.bin_entries + (size_t)b * p.bin_cap;
 #pragma unroll
-        for (int k = 0; k < kMaxK; ++k) {
-            if (k < K && slab[k] >= 0) {
-                const size_t at = (size_t)off[slab[k]] + base[slab[k]] + pos[k];
-                list[at] = make_uint2((unsigned int)row * (unsigned int)K + (unsigned int)k, __float_as_uint(prob[k]));
+        for (int j = 0; j < kMaxK; ++j) {
+            if (slab[j] >= 0) {
+                const int k = lane_c + j * gs;
+                const size_t at = (size_t)off[slab[j]] + base[slab[j]] + pos[j];
+                list[at] = make_uint2((unsigned int)row * (unsigned int)K + (unsigned int)k, __float_as_uint(prob[j]));
             }
         }
     }
