@@ -170,6 +170,14 @@ size_t bin_scratch_bytes(int B, int N, int G, int D, int Q, int K) {
     return round256((size_t)3 * B * fda::kMaxSlabs * sizeof(unsigned int)) + (size_t)B * cap * sizeof(uint2);
 }
 
+// Rows of exactly four lanes with two 16-byte reductions per lane (D = 32, 16-bit value): neighbouring
+// rows scatter as a team so that every reduction request covers a whole 128-byte line of the image.
+template <typename VT>
+bool pair_rows(const fda::Problem &p) {
+    if (const char *e = std::getenv("FDA_PAIR_ROWS")) if (std::atoi(e) == 0) return false;
+    return fda::Vec16<VT>::kCPL == 8 && p.gs_log2 == 2 && p.lpg == 4;
+}
+
 template <typename VT, typename PT>
 int launch_binned(fda::Problem p, cudaStream_t st) {
     const size_t counter_bytes = (size_t)3 * p.B * fda::kMaxSlabs * sizeof(unsigned int);
@@ -189,7 +197,8 @@ int launch_binned(fda::Problem p, cudaStream_t st) {
     }
     // x: blocks striding over one slab's list; y: slab (slabs run one after the other); z: batch element
     const dim3 grid(592, fda::kMaxSlabs, (unsigned)p.B);
-    fda::fda_backward_binned_kernel<VT, PT><<<grid, fda::kThreads, 0, st>>>(p);
+    if (pair_rows<VT>(p)) fda::fda_backward_binned_kernel<VT, PT, true><<<grid, fda::kThreads, 0, st>>>(p);
+    else fda::fda_backward_binned_kernel<VT, PT, false><<<grid, fda::kThreads, 0, st>>>(p);
     e = cudaGetLastError();
     return e == cudaSuccess ? FDA_OK : cuda_fail(e);
 }
@@ -201,7 +210,7 @@ int launch_backward(fda::Problem p, cudaStream_t st) {
     p.row_stride = padded_stride(5 * p.LK);
     const int threads = pick_threads(p, p.row_stride);
     const size_t smem = (size_t)(threads >> p.gs_log2) * p.row_stride * sizeof(float);
-    auto kern = fda::fda_backward_kernel<VT, PT>;
+    auto kern = pair_rows<VT>(p) ? fda::fda_backward_kernel<VT, PT, true> : fda::fda_backward_kernel<VT, PT, false>;
     if (int rc = ensure_smem(reinterpret_cast<const void *>(kern), smem)) return rc;
     kern<<<row_grid(p, threads), threads, smem, st>>>(p);
     const cudaError_t e = cudaGetLastError();

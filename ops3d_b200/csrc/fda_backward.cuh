@@ -51,16 +51,37 @@ struct RowGrad {
             s[r][0] = f.x; s[r][1] = f.y; s[r][2] = f.z; s[r][3] = f.w;
         }
     }
+    // Paired layout (two rows of 4 lanes form a team of 8): s[0] = channels 4*tl.. of the EVEN row of the
+    // team, s[1] = the same channels of the ODD row, tl = lane within the team.  `go_even` / `go_odd` may be
+    // null when that row does not exist.
+    __device__ __forceinline__ void load_paired(const VT *go_own, int lane_c, bool active, const VT *go_even,
+                                                const VT *go_odd, int tl, uint64_t pol) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (active) raw = ldg16_hint(go_own + (size_t)lane_c * CPL, pol);
+        Vec16<VT>::unpack(raw, d);
+        float4 e = make_float4(0.f, 0.f, 0.f, 0.f), o = e;
+        if (go_even) e = load4<VT>(go_even + 4 * tl);
+        if (go_odd) o = load4<VT>(go_odd + 4 * tl);
+        s[0][0] = e.x; s[0][1] = e.y; s[0][2] = e.z; s[0][3] = e.w;
+        s[NRED - 1][0] = o.x; s[NRED - 1][1] = o.y; s[NRED - 1][2] = o.z; s[NRED - 1][3] = o.w;
+    }
 };
 
 // Backward of one sampling point for the lanes of one row: gathers the 8 corners, scatters
 // a*w*grad_out into the fp32 image, and returns (summed over the row's lanes) the gradients w.r.t.
 // the normalised coordinates and dalpha = <sample, grad_out>.  Must be called by all 32 lanes.
-template <typename VT>
+//
+// kPair (rows of exactly 4 lanes, 32 fp32 = 128 bytes of image per corner): two neighbouring rows
+// form a team of 8 lanes and scatter together -- first the even row's corner, then the odd row's,
+// each as 8 x 16 contiguous bytes, so that one reduction request to L2 covers a whole 128-byte line
+// instead of two half-line requests.  acc_even / acc_odd are the two rows' image bases (head offset
+// included, lane offset excluded); weight and offset of the partner row's corner come by shuffle.
+template <typename VT, bool kPair>
 __device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, float x, float y, float z, float a,
                                                const VT *lvl, float *acc_lvl, const RowGrad<VT> &go, int red_stride,
                                                bool active, int gs, uint64_t pol_v, uint64_t pol_g,
-                                               float &gx_out, float &gy_out, float &gz_out, float &da_out) {
+                                               float &gx_out, float &gy_out, float &gz_out, float &da_out,
+                                               float *acc_even = nullptr, float *acc_odd = nullptr) {
     constexpr int CPL = Vec16<VT>::kCPL;
     constexpr int NRED = CPL / 4;
     PointGeom pg;
@@ -77,7 +98,21 @@ __device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, floa
     for (int n = 0; n < 8; ++n) {
         const float w = (pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2];
         const float aw = a * w;
-        if (in[n]) {
+        if (kPair) {
+            const unsigned lane = threadIdx.x & 31u;
+            const bool odd = (lane >> 2) & 1u;
+            const uint32_t code = in[n] ? pg.off[n] : 0x80000000u;  // offsets stay below 2^31
+            const uint32_t code_p = __shfl_xor_sync(0xffffffffu, code, 4);
+            const float aw_p = __shfl_xor_sync(0xffffffffu, aw, 4);
+            const uint32_t code_e = odd ? code_p : code, code_o = odd ? code : code_p;
+            const float aw_e = odd ? aw_p : aw, aw_o = odd ? aw : aw_p;
+            const unsigned tl4 = (lane & 7u) * 4u;
+            if (!(code_e >> 31))
+                red_add_f32x4_hint(acc_even + code_e + tl4, aw_e * go.s[0][0], aw_e * go.s[0][1], aw_e * go.s[0][2], aw_e * go.s[0][3], pol_g);
+            if (!(code_o >> 31))
+                red_add_f32x4_hint(acc_odd + code_o + tl4, aw_o * go.s[NRED - 1][0], aw_o * go.s[NRED - 1][1], aw_o * go.s[NRED - 1][2],
+                                   aw_o * go.s[NRED - 1][3], pol_g);
+        } else if (in[n]) {
             float *dst = acc_lvl + pg.off[n];
 #pragma unroll
             for (int r = 0; r < NRED; ++r)
@@ -119,7 +154,7 @@ __device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, floa
     da_out = da;
 }
 
-template <typename VT, typename PT>
+template <typename VT, typename PT, bool kPair>
 __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_kernel(const Problem p) {
     constexpr int CPL = Vec16<VT>::kCPL;
     __shared__ LevelGeom geom[kMaxLevels];
@@ -195,8 +230,18 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
     float *accum_b = p.accum + head_elem + (size_t)lane_c * 4;
 
     RowGrad<VT> go;
-    go.load(static_cast<const VT *>(p.grad_out) + ((size_t)b * p.rows_per_b + (row_ok ? row : 0)) * (size_t)p.D,
-            lane_c, p.lpg, active, pol_stream);
+    const VT *go_rows = static_cast<const VT *>(p.grad_out) + (size_t)b * p.rows_per_b * (size_t)p.D;
+    float *acc_even = nullptr, *acc_odd = nullptr;  // kPair: image bases of the two rows of this lane's team
+    if (kPair) {
+        const int row_e = row & ~1, row_o = row | 1;  // rows of a team are neighbours; an odd last row has no partner
+        go.load_paired(go_rows + (size_t)(row_ok ? row : 0) * p.D, lane_c, active,
+                       row_e < p.rows_per_b ? go_rows + (size_t)row_e * p.D : nullptr,
+                       row_o < p.rows_per_b ? go_rows + (size_t)row_o * p.D : nullptr, lane & 7, pol_stream);
+        acc_even = p.accum + (size_t)b * p.N * p.GD + (size_t)(row_e % p.G) * p.D;
+        acc_odd = p.accum + (size_t)b * p.N * p.GD + (size_t)(row_o % p.G) * p.D;
+    } else {
+        go.load(go_rows + (size_t)(row_ok ? row : 0) * p.D, lane_c, p.lpg, active, pol_stream);
+    }
     const int red_stride = 4 * p.lpg;
 
     for (int j = 0; j < nchunk; ++j) {
@@ -217,8 +262,10 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
         float gxs[4], gys[4], gzs[4], das[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t)
-            point_backward<VT>(lv, p.GD, xs[t], ys[t], zs[t], es[t] * inv, lvl, acc_lvl, go, red_stride, active, gs,
-                               pol_v, pol_g, gxs[t], gys[t], gzs[t], das[t]);
+            point_backward<VT, kPair>(lv, p.GD, xs[t], ys[t], zs[t], es[t] * inv, lvl, acc_lvl, go, red_stride, active, gs,
+                                      pol_v, pol_g, gxs[t], gys[t], gzs[t], das[t],
+                                      kPair ? acc_even + (size_t)lv.start * p.GD : nullptr,
+                                      kPair ? acc_odd + (size_t)lv.start * p.GD : nullptr);
         __syncwarp();  // every lane of the row has read this chunk's coordinates
         if (lane_c == 0) {
             *reinterpret_cast<float4 *>(trow + 12 * j) = make_float4(gxs[0], gys[0], gzs[0], gxs[1]);

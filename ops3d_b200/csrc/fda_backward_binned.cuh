@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(kThreads) fda_bin_fill_kernel(const Problem p)
     }
 }
 
-template <typename VT, typename PT>
+template <typename VT, typename PT, bool kPair>
 __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_binned_kernel(const Problem p) {
     constexpr int CPL = Vec16<VT>::kCPL;
     __shared__ BinPlan plan;
@@ -261,9 +261,25 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
         const VT *lvl = static_cast<const VT *>(p.value) + head_elem + (size_t)lane_c * CPL;
         float *acc_lvl = p.accum + head_elem + (size_t)lane_c * 4;
         RowGrad<VT> go;
-        go.load(static_cast<const VT *>(p.grad_out) + grow * (size_t)p.D, lane_c, p.lpg, active, pol_stream);
+        const VT *go_own = static_cast<const VT *>(p.grad_out) + grow * (size_t)p.D;
+        float *acc_even = nullptr, *acc_odd = nullptr;
+        if (kPair) {
+            // the partner entry of this lane's team is an arbitrary other row: exchange row pointers by shuffle
+            const unsigned long long mine_go = have ? reinterpret_cast<unsigned long long>(go_own) : 0ull;
+            const unsigned long long mine_acc = reinterpret_cast<unsigned long long>(p.accum + head_elem);
+            const unsigned long long other_go = __shfl_xor_sync(0xffffffffu, mine_go, 4);
+            const unsigned long long other_acc = __shfl_xor_sync(0xffffffffu, mine_acc, 4);
+            const bool odd = ((tid & 31) >> 2) & 1;
+            go.load_paired(go_own, lane_c, active, reinterpret_cast<const VT *>(odd ? other_go : mine_go),
+                           reinterpret_cast<const VT *>(odd ? mine_go : other_go), tid & 7, pol_stream);
+            acc_even = reinterpret_cast<float *>(odd ? other_acc : mine_acc);
+            acc_odd = reinterpret_cast<float *>(odd ? mine_acc : other_acc);
+        } else {
+            go.load(go_own, lane_c, p.lpg, active, pol_stream);
+        }
         float gx, gy, gz, da;
-        point_backward<VT>(lv, p.GD, x, y, z, a, lvl, acc_lvl, go, red_stride, active, gs, pol_keep, pol_keep, gx, gy, gz, da);
+        point_backward<VT, kPair>(lv, p.GD, x, y, z, a, lvl, acc_lvl, go, red_stride, active, gs, pol_keep, pol_keep,
+                                  gx, gy, gz, da, acc_even, acc_odd);
         if (have && lane_c == 0) {
             PT *gr = static_cast<PT *>(p.grad_packed) + grow * (size_t)(4 * LK);
             const int i = lvl_first + k;
