@@ -361,11 +361,13 @@ def run_ours(args, cfg):
         torch.cuda.synchronize()
 
     events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    launches0 = capi.KERNEL_LAUNCHES
     t_host0 = time.perf_counter()
     for ev in events:
         step(ev)
     torch.cuda.synchronize()
     t_host1 = time.perf_counter()
+    gpu_launches = capi.KERNEL_LAUNCHES - launches0
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
@@ -466,8 +468,7 @@ def run_ours(args, cfg):
             "roofline": roofline,
             "e2e": {"value": (B / (e2e_ms * 1e-3)) if e2e_ms else None, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "gpu_launches": args.steps * ((1 + 2 * B * (len(reducer_passes) if reducer_passes else 1)) if use_peer
-                                          else (3 if vdt != torch.float32 else 2)),
+            "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
         if ref_cuda is not None:

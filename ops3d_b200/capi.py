@@ -25,6 +25,15 @@ NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
 
 _lib = None
 
+# Kernels launched through this module since import (this library's own kernels only; zero-fills are
+# cudaMemsetAsync calls and are not counted).  Benchmarks read the difference around a timed region.
+KERNEL_LAUNCHES = 0
+
+
+def _count(n: int):
+    global KERNEL_LAUNCHES
+    KERNEL_LAUNCHES += n
+
 
 class FdaError(RuntimeError):
     def __init__(self, status: int, message: str):
@@ -100,6 +109,7 @@ def forward(value, shapes, lsi, packed, K, im2col_step=64, use_reg=True, out=Non
             value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), out.data_ptr(),
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype],
             im2col_step, 8, 0, int(bool(use_reg)), _stream(value)))
+    _count(1)
     return out
 
 
@@ -132,6 +142,8 @@ def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value
             workspace.numel() * workspace.element_size() if workspace is not None else 0,
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype],
             im2col_step, 1, 0, _stream(value)))
+    # scatter kernel (+ count, scan, fill, binned kernels when the workspace includes binning scratch) + cast
+    _count(1 + (4 if scratch_bytes(value, packed, K) else 0) + (1 if value.dtype != torch.float32 else 0))
     return grad_value, grad_packed
 
 
@@ -145,6 +157,7 @@ def backward_accumulate(value, shapes, lsi, packed, grad_out, K, accum, grad_pac
             value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
             accum.data_ptr(), grad_packed.data_ptr(),
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype], im2col_step, _stream(value)))
+    _count(1)
     return grad_packed
 
 
@@ -161,6 +174,7 @@ def backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, g
             level_begin, level_end, flags,
             scratch.data_ptr() if scratch is not None else None,
             scratch.numel() * scratch.element_size() if scratch is not None else 0, _stream(value)))
+    _count(1 + (4 if (scratch is not None and scratch_bytes(value, packed, K)) else 0))
     return grad_packed
 
 
@@ -168,6 +182,7 @@ def cast_grad_value(accum, grad_value):
     with torch.cuda.device(accum.device):
         check(load().fda_cast_grad_value(accum.data_ptr(), grad_value.data_ptr(), accum.numel(),
                                          DTYPE_CODE[grad_value.dtype], _stream(accum)))
+    _count(1 if grad_value.dtype != torch.float32 else 0)
     return grad_value
 
 
@@ -181,6 +196,7 @@ def backward_noalloc(value, shapes, lsi, packed, grad_out, K, grad_value, grad_p
             value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
             grad_value.data_ptr(), grad_packed.data_ptr(),
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype], im2col_step, _stream(value)))
+    _count(1 + (1 if value.dtype != torch.float32 else 0))
     return grad_value, grad_packed
 
 
@@ -195,6 +211,7 @@ def peer_reduce_cast(image_ptrs, output_ptrs, rank, num_elements, dtype, device,
     with torch.cuda.device(device):
         check(load().fda_peer_reduce_cast(imgs, outs, world, rank, num_elements, DTYPE_CODE[dtype],
                                           torch.cuda.current_stream(device).cuda_stream))
+    _count(1)
 
 
 def multimem_reduce_cast(mc_image_ptr, mc_output_ptr, world, rank, num_elements, dtype, device, byte_offsets=(0, 0)):
@@ -202,6 +219,7 @@ def multimem_reduce_cast(mc_image_ptr, mc_output_ptr, world, rank, num_elements,
     with torch.cuda.device(device):
         check(load().fda_multimem_reduce_cast(mc_image_ptr + byte_offsets[0], mc_output_ptr + byte_offsets[1], world, rank,
                                               num_elements, DTYPE_CODE[dtype], torch.cuda.current_stream(device).cuda_stream))
+    _count(1)
 
 
 def peer_push_partials(image_ptr, staging_ptrs, slot_stride, rank, num_elements, device):
@@ -212,6 +230,7 @@ def peer_push_partials(image_ptr, staging_ptrs, slot_stride, rank, num_elements,
     with torch.cuda.device(device):
         check(load().fda_peer_push_partials(image_ptr, st, slot_stride, world, rank, num_elements,
                                             torch.cuda.current_stream(device).cuda_stream))
+    _count(1)
 
 
 def peer_reduce_staged_cast(image_ptr, staging_ptr, slot_stride, output_ptrs, rank, num_elements, dtype, device):
@@ -220,3 +239,4 @@ def peer_reduce_staged_cast(image_ptr, staging_ptr, slot_stride, output_ptrs, ra
     with torch.cuda.device(device):
         check(load().fda_peer_reduce_staged_cast(image_ptr, staging_ptr, slot_stride, outs, world, rank, num_elements,
                                                  DTYPE_CODE[dtype], torch.cuda.current_stream(device).cuda_stream))
+    _count(1)
