@@ -26,7 +26,6 @@ namespace fda {
 
 constexpr int kMaxLevels = 5;
 constexpr int kThreads = 256;
-constexpr int kWarpsPerBlock = kThreads / 32;
 
 struct LevelGeom {
     int D, H, W;
@@ -237,14 +236,6 @@ template <> __device__ __forceinline__ void store4_stream<__half>(__half *p, con
     __stcs(reinterpret_cast<uint2 *>(p), make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b)));
 }
 
-// 16-byte read-only gather load.
-__device__ __forceinline__ uint4 ldg16(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
-
-// fp32 x4 reduction into global memory (one 16-byte L2 atomic operation, no return value).
-__device__ __forceinline__ void red_add_f32x4(float *p, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 // L2 eviction-priority policies.  The gather re-reads small pyramid levels hundreds of times while
 // the largest level and the per-query rows stream through once; marking the former "evict last"
 // and the latter "evict first" keeps the re-used levels resident in the 126 MB L2.
@@ -263,12 +254,14 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
     return pol;
 }
+// 16-byte read-only gather load with an L2 eviction policy.
 __device__ __forceinline__ uint4 ldg16_hint(const void *p, uint64_t pol) {
     uint4 r;
     asm("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
         : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p), "l"(pol));
     return r;
 }
+// fp32 x4 reduction into global memory (one 16-byte L2 atomic operation, no return value).
 __device__ __forceinline__ void red_add_f32x4_hint(float *p, float a, float b, float c, float d, uint64_t pol) {
     asm volatile("red.global.add.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
                  ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d), "l"(pol) : "memory");
