@@ -58,7 +58,7 @@ METRIC = "fwd+bwd samples/s (fwd samples/s and achieved GB/s vs HBM roofline bes
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per full-size launch of the backward kernels of
 # config 5, from the ncu captures summarised under profiles/: measured on the reduced case
 # (--batch 1 --queries 74752, 1/16 of the rows over the same per-batch-element volume) and scaled x16.
-NCU_BACKWARD_TRAFFIC_BYTES = {5: 16 * (3.36e9 + 3.10e9)}
+NCU_BACKWARD_TRAFFIC_BYTES = {5: 16 * (3.16e9 + 3.09e9)}
 
 
 # ---------------------------------------------------------------------------------------------
