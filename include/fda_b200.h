@@ -163,6 +163,7 @@ int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_element
 #define FDA_BWD_ZERO_IMAGE 1
 #define FDA_BWD_RESUME 2
 #define FDA_BWD_FINALIZE 4
+#define FDA_BWD_BINNED_DONE 8 /* the largest level was already scattered with fda_backward_binned_part */
 int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
                                    const void *sampling_loc_attn, const void *grad_output,
                                    float *accum, void *grad_sampling_loc_attn,
@@ -170,6 +171,29 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
                                    int num_query, int num_points, int value_dtype, int packed_dtype,
                                    int im2col_step, int level_begin, int level_end, int flags,
                                    void *scratch, size_t scratch_bytes, void *stream);
+
+/*
+ * The slab-binned scatter of the largest level in `parts` launches, so that a multi-GPU caller can
+ * exchange the z-range of the image that a launch has finished while the next launch runs.
+ * fda_backward_bin_plan answers, from a HOST copy of spatial_shapes, whether binning applies to a
+ * problem (return value 1) and how: the level, its number of slabs S and planes per slab `depth`.
+ * Launch `part` (0-based) covers slabs [S*part/parts, S*(part+1)/parts); after it, the image planes
+ * [first_slab*depth, min(last_slab_end*depth, D_level)) of that level are final (the plane above is
+ * still written by the next slab).  Part 0 also builds the slab lists and, with FDA_BWD_ZERO_IMAGE,
+ * zero-fills the image.  After the last part call fda_backward_accumulate_levels over all levels
+ * with FDA_BWD_RESUME | FDA_BWD_FINALIZE | FDA_BWD_BINNED_DONE and the same scratch.  Returns
+ * FDA_ERR_WORKSPACE when scratch is missing or binning does not apply to the problem.
+ * No counterpart in the reference.
+ */
+int fda_backward_bin_plan(const int64_t *spatial_shapes_host, int num_levels, int batch, int num_value, int num_heads,
+                          int head_dim, int num_query, int num_points, int *level, int *slabs, int *depth);
+int fda_backward_binned_part(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                             const void *sampling_loc_attn, const void *grad_output,
+                             float *accum, void *grad_sampling_loc_attn,
+                             int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                             int num_query, int num_points, int value_dtype, int packed_dtype,
+                             int im2col_step, int part, int parts, int flags,
+                             void *scratch, size_t scratch_bytes, void *stream);
 
 /*
  * Cross-GPU sum + cast of the fp32 images over peer (NVLink) memory, for the query-sharded

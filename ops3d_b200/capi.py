@@ -18,9 +18,9 @@ EXPORTS = (
     "fda_status_string", "fda_last_cuda_error", "fda_version", "fda_forward",
     "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
-    "fda_peer_push_partials", "fda_peer_reduce_staged_cast",
+    "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
 )
-BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE = 1, 2, 4
+BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE = 1, 2, 4, 8
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
 
 _lib = None
@@ -66,6 +66,10 @@ def load() -> ctypes.CDLL:
     lib.fda_backward_accumulate.restype = i
     lib.fda_backward_accumulate_levels.argtypes = [vp] * 7 + [i] * 13 + [vp, sz, vp]
     lib.fda_backward_accumulate_levels.restype = i
+    lib.fda_backward_bin_plan.argtypes = [vp] + [i] * 7 + [vp, vp, vp]
+    lib.fda_backward_bin_plan.restype = i
+    lib.fda_backward_binned_part.argtypes = [vp] * 7 + [i] * 13 + [vp, sz, vp]
+    lib.fda_backward_binned_part.restype = i
     lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
     lib.fda_cast_grad_value.restype = i
     lib.fda_backward_noalloc.argtypes = [vp] * 7 + [i] * 10 + [vp]
@@ -174,7 +178,33 @@ def backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, g
             level_begin, level_end, flags,
             scratch.data_ptr() if scratch is not None else None,
             scratch.numel() * scratch.element_size() if scratch is not None else 0, _stream(value)))
-    _count(1 + (4 if (scratch is not None and scratch_bytes(value, packed, K)) else 0))
+    binned_here = scratch is not None and scratch_bytes(value, packed, K) and not (flags & BWD_BINNED_DONE)
+    _count(1 + (4 if binned_here else 0))
+    return grad_packed
+
+
+def bin_plan(shapes_host, value_shape, num_query, K):
+    """``fda_backward_bin_plan`` on a host copy of the shapes: ``None`` when binning does not apply, else
+    ``(level, slabs, planes_per_slab)``."""
+    sh = torch.as_tensor(shapes_host).cpu().long().contiguous()
+    B, N, G, D = value_shape
+    lvl, slabs, depth = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+    ok = load().fda_backward_bin_plan(sh.data_ptr(), sh.shape[0], B, N, G, D, num_query, K,
+                                      ctypes.addressof(lvl), ctypes.addressof(slabs), ctypes.addressof(depth))
+    return (lvl.value, slabs.value, depth.value) if ok else None
+
+
+def backward_binned_part(value, shapes, lsi, packed, grad_out, K, accum, grad_packed, part, parts, flags, scratch,
+                         im2col_step=64):
+    """``fda_backward_binned_part``: slab group ``part`` of ``parts`` of the largest level."""
+    B, N, G, D, L, Q = _dims(value, shapes, packed)
+    with torch.cuda.device(value.device):
+        check(load().fda_backward_binned_part(
+            value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(), grad_out.data_ptr(),
+            accum.data_ptr(), grad_packed.data_ptr(),
+            B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype], im2col_step,
+            part, parts, flags, scratch.data_ptr(), scratch.numel() * scratch.element_size(), _stream(value)))
+    _count(1 + (3 if part == 0 else 0))
     return grad_packed
 
 

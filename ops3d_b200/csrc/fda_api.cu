@@ -90,6 +90,8 @@ fda::Problem make_problem(const Shape &s) {
     p.l2_keep_bytes = l2_keep_budget();
     p.level_mask = (1 << s.L) - 1;
     p.finalize = 1;
+    p.slab_part = 0;
+    p.slab_parts = 1;
     return p;
 }
 
@@ -172,40 +174,78 @@ size_t bin_scratch_bytes(int B, int N, int G, int D, int Q, int K) {
 
 // Rows of exactly four lanes with two 16-byte reductions per lane (D = 32, 16-bit value): neighbouring
 // rows scatter as a team so that every reduction request covers a whole 128-byte line of the image.
+unsigned long long bin_slab_bytes_setting() {
+    double slab_mb = 16.0;  // share of the fp32 image per slab (value rows of the slab add half of that); 8-16 MB measured best on B200
+    if (const char *e = std::getenv("FDA_BIN_SLAB_MB")) slab_mb = std::atof(e);
+    unsigned long long b = (unsigned long long)(slab_mb * 1048576.0);
+    return b < 4096 ? 4096 : b;
+}
+
+// Point the problem at the caller's binning scratch when it is present and large enough.
+void attach_bin_scratch(fda::Problem &p, const Shape &s, void *scratch, size_t scratch_bytes) {
+    const size_t need = bin_scratch_bytes(s.B, s.N, s.G, s.D, s.Q, s.K);
+    if (need == 0 || !scratch || scratch_bytes < need || !aligned16(scratch)) return;
+    p.bin_allowed = 1;
+    p.bin_counters = static_cast<unsigned int *>(scratch);
+    p.bin_entries = reinterpret_cast<uint2 *>(static_cast<char *>(scratch) +
+                                              round256((size_t)3 * s.B * fda::kMaxSlabs * sizeof(unsigned int)));
+    p.bin_cap = (unsigned long long)s.Q * s.G * s.K;
+    p.bin_slab_bytes = bin_slab_bytes_setting();
+}
+
 template <typename VT>
 bool pair_rows(const fda::Problem &p) {
     if (const char *e = std::getenv("FDA_PAIR_ROWS")) if (std::atoi(e) == 0) return false;
     return fda::Vec16<VT>::kCPL == 8 && p.gs_log2 == 2 && p.lpg == 4;
 }
 
-template <typename VT, typename PT>
-int launch_binned(fda::Problem p, cudaStream_t st) {
+// Sort the largest level's points into slab lists (zero the counters, count, scan, fill).
+template <typename PT>
+int launch_bin_prepare(const fda::Problem &p, cudaStream_t st) {
     const size_t counter_bytes = (size_t)3 * p.B * fda::kMaxSlabs * sizeof(unsigned int);
     cudaError_t e = cudaMemsetAsync(p.bin_counters, 0, counter_bytes, st);
     if (e != cudaSuccess) return cuda_fail(e);
     const dim3 rows_grid((unsigned)((p.rows_per_b + 255) / 256), (unsigned)p.B, 1);
     fda::fda_bin_count_kernel<PT><<<rows_grid, 256, 0, st>>>(p);
     fda::fda_bin_scan_kernel<<<(unsigned)((p.B + 127) / 128), 128, 0, st>>>(p);
-    {
-        fda::Problem q = p;
-        q.row_stride = padded_stride(4 * p.LK);
-        const int threads = pick_threads(q, q.row_stride);
-        const size_t smem = (size_t)(threads >> q.gs_log2) * q.row_stride * sizeof(float);
-        auto kern = fda::fda_bin_fill_kernel<PT>;
-        if (int rc = ensure_smem(reinterpret_cast<const void *>(kern), smem)) return rc;
-        kern<<<row_grid(q, threads), threads, smem, st>>>(q);
-    }
-    // x: blocks striding over one slab's list; y: slab (slabs run one after the other); z: batch element
-    const dim3 grid(592, fda::kMaxSlabs, (unsigned)p.B);
-    if (pair_rows<VT>(p)) fda::fda_backward_binned_kernel<VT, PT, true><<<grid, fda::kThreads, 0, st>>>(p);
-    else fda::fda_backward_binned_kernel<VT, PT, false><<<grid, fda::kThreads, 0, st>>>(p);
+    fda::Problem q = p;
+    q.row_stride = padded_stride(4 * p.LK);
+    const int threads = pick_threads(q, q.row_stride);
+    const size_t smem = (size_t)(threads >> q.gs_log2) * q.row_stride * sizeof(float);
+    auto kern = fda::fda_bin_fill_kernel<PT>;
+    if (int rc = ensure_smem(reinterpret_cast<const void *>(kern), smem)) return rc;
+    kern<<<row_grid(q, threads), threads, smem, st>>>(q);
     e = cudaGetLastError();
     return e == cudaSuccess ? FDA_OK : cuda_fail(e);
 }
 
+// The slab-by-slab scatter of the slabs selected by p.slab_part / p.slab_parts.
+template <typename VT, typename PT>
+int launch_binned_slabs(const fda::Problem &p, cudaStream_t st) {
+    // x: blocks striding over one slab's list; y: slab (slabs run one after the other); z: batch element
+    const dim3 grid(592, fda::kMaxSlabs, (unsigned)p.B);
+    if (pair_rows<VT>(p)) fda::fda_backward_binned_kernel<VT, PT, true><<<grid, fda::kThreads, 0, st>>>(p);
+    else fda::fda_backward_binned_kernel<VT, PT, false><<<grid, fda::kThreads, 0, st>>>(p);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FDA_OK : cuda_fail(e);
+}
+
+template <typename VT, typename PT>
+int launch_binned(fda::Problem p, cudaStream_t st) {
+    if (int rc = launch_bin_prepare<PT>(p, st)) return rc;
+    return launch_binned_slabs<VT, PT>(p, st);
+}
+
+template <typename VT, typename PT>
+int launch_binned_part(fda::Problem p, cudaStream_t st) {
+    if (p.slab_part == 0)
+        if (int rc = launch_bin_prepare<PT>(p, st)) return rc;
+    return launch_binned_slabs<VT, PT>(p, st);
+}
+
 template <typename VT, typename PT>
 int launch_backward(fda::Problem p, cudaStream_t st) {
-    if (p.bin_allowed)
+    if (p.bin_allowed && !p.binned_elsewhere)
         if (int rc = launch_binned<VT, PT>(p, st)) return rc;
     p.row_stride = padded_stride(5 * p.LK);
     const int threads = pick_threads(p, p.row_stride);
@@ -312,19 +352,53 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
     p.resume = (flags & FDA_BWD_RESUME) ? 1 : 0;
     p.finalize = (flags & FDA_BWD_FINALIZE) ? 1 : 0;
     // slab-binned handling of the largest level, when the caller gave scratch for it
-    const size_t need = bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points);
-    if (need > 0 && scratch && scratch_bytes >= need && aligned16(scratch)) {
-        p.bin_allowed = 1;
-        p.bin_counters = static_cast<unsigned int *>(scratch);
-        p.bin_entries = reinterpret_cast<uint2 *>(static_cast<char *>(scratch) +
-                                                  round256((size_t)3 * batch * fda::kMaxSlabs * sizeof(unsigned int)));
-        p.bin_cap = (unsigned long long)num_query * num_heads * num_points;
-        double slab_mb = 16.0;  // share of the fp32 image per slab (value rows of the slab add half of that); 8-16 MB measured best on B200
-        if (const char *e = std::getenv("FDA_BIN_SLAB_MB")) slab_mb = std::atof(e);
-        p.bin_slab_bytes = (unsigned long long)(slab_mb * 1048576.0);
-        if (p.bin_slab_bytes < 4096) p.bin_slab_bytes = 4096;
-    }
+    attach_bin_scratch(p, s, scratch, scratch_bytes);
+    p.binned_elsewhere = (flags & FDA_BWD_BINNED_DONE) ? 1 : 0;
+    if (p.binned_elsewhere && !p.bin_allowed) return FDA_ERR_WORKSPACE;
     return FDA_DISPATCH(value_dtype, packed_dtype, (launch_backward<VT, PT>(p, st)));
+}
+
+int fda_backward_bin_plan(const int64_t *spatial_shapes_host, int num_levels, int batch, int num_value, int num_heads,
+                          int head_dim, int num_query, int num_points, int *level, int *slabs, int *depth) {
+    if (!spatial_shapes_host || num_levels < 1 || num_levels > fda::kMaxLevels) return 0;
+    if (bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points) == 0) return 0;
+    const fda::BinPlan plan = fda::bin_plan_from(spatial_shapes_host, num_levels, num_heads * head_dim, l2_keep_budget(),
+                                                 bin_slab_bytes_setting(), (1 << num_levels) - 1, 1);
+    if (level) *level = plan.level;
+    if (slabs) *slabs = plan.slabs;
+    if (depth) *depth = plan.depth;
+    return plan.enabled;
+}
+
+int fda_backward_binned_part(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                             const void *sampling_loc_attn, const void *grad_output,
+                             float *accum, void *grad_sampling_loc_attn,
+                             int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                             int num_query, int num_points, int value_dtype, int packed_dtype,
+                             int im2col_step, int part, int parts, int flags,
+                             void *scratch, size_t scratch_bytes, void *stream) {
+    if (!value || !spatial_shapes || !level_start_index || !sampling_loc_attn || !grad_output || !accum || !grad_sampling_loc_attn)
+        return FDA_ERR_NULL_POINTER;
+    const Shape s{batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, packed_dtype};
+    if (int rc = validate(s, im2col_step)) return rc;
+    if (parts < 1 || part < 0 || part >= parts) return FDA_ERR_BAD_SHAPE;
+    if (!aligned16(value) || !aligned16(sampling_loc_attn) || !aligned16(grad_output) || !aligned16(accum) ||
+        !aligned16(grad_sampling_loc_attn))
+        return FDA_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    fda::Problem p = make_problem(s);
+    p.value = value; p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn;
+    p.grad_out = grad_output; p.accum = accum; p.grad_packed = grad_sampling_loc_attn;
+    attach_bin_scratch(p, s, scratch, scratch_bytes);
+    if (!p.bin_allowed) return FDA_ERR_WORKSPACE;
+    p.slab_part = part;
+    p.slab_parts = parts;
+    if ((flags & FDA_BWD_ZERO_IMAGE) && part == 0) {
+        const size_t n = (size_t)batch * num_value * num_heads * head_dim;
+        cudaError_t e = cudaMemsetAsync(accum, 0, n * sizeof(float), st);
+        if (e != cudaSuccess) return cuda_fail(e);
+    }
+    return FDA_DISPATCH(value_dtype, packed_dtype, (launch_binned_part<VT, PT>(p, st)));
 }
 
 int fda_backward_accumulate(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,

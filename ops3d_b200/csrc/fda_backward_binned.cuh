@@ -208,8 +208,11 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
         lv_s = level_geom_of(p, plan.level);
     }
     __syncthreads();
-    const int slab = blockIdx.y, b = blockIdx.z;
-    if (!plan.enabled || slab >= plan.slabs) return;
+    const int b = blockIdx.z;
+    if (!plan.enabled) return;
+    const int slab_first = plan.slabs * p.slab_part / p.slab_parts, slab_end = plan.slabs * (p.slab_part + 1) / p.slab_parts;
+    const int slab = slab_first + (int)blockIdx.y;
+    if (slab >= slab_end) return;
     const LevelGeom lv = lv_s;
     const unsigned int count = p.bin_counters[(size_t)b * kMaxSlabs + slab];
     const unsigned int offset = p.bin_counters[(size_t)(p.B + b) * kMaxSlabs + slab];

@@ -63,28 +63,32 @@ struct Problem {
     unsigned int *bin_counters;          // [3][B][kMaxSlabs]: count, offset, cursor
     uint2 *bin_entries;                  // [B][bin_cap]: {row * K + k, soft-max probability}
     unsigned long long bin_cap;          // entries per batch element = rows_per_b * K
+    int slab_part, slab_parts;           // the binned kernel of this launch covers slabs [S*part/parts, S*(part+1)/parts)
+    int binned_elsewhere;                // the binned launches for this call were issued separately (plain kernel only)
 };
 
 constexpr int kMaxSlabs = 64;
 
 // Which level (if any) is handled slab by slab, and how it is cut along z.  A pure function of the
-// shapes and launch parameters, so every kernel of one backward call derives the same plan.
+// shapes and launch parameters, so every kernel of one backward call -- and the host, when it has a
+// host copy of the shapes -- derives the same plan.
 struct BinPlan {
     int level, enabled, slabs, depth;
 };
-__device__ __forceinline__ BinPlan make_bin_plan(const Problem &p) {
+__host__ __device__ inline BinPlan bin_plan_from(const int64_t *shapes, int L, int GD, unsigned long long l2_keep_bytes,
+                                                 unsigned long long slab_bytes, int level_mask, int allowed) {
     BinPlan plan;
     plan.level = 0; plan.enabled = 0; plan.slabs = 1; plan.depth = 1;
-    if (!p.bin_allowed) return plan;
+    if (!allowed) return plan;
     unsigned long long best = 0;
-    for (int l = 0; l < p.L; ++l) {
-        const unsigned long long c = (unsigned long long)p.shapes[3 * l] * p.shapes[3 * l + 1] * p.shapes[3 * l + 2];
+    for (int l = 0; l < L; ++l) {
+        const unsigned long long c = (unsigned long long)shapes[3 * l] * shapes[3 * l + 1] * shapes[3 * l + 2];
         if (c > best) { best = c; plan.level = l; }
     }
-    const unsigned long long image_bytes = best * (unsigned long long)p.GD * 4ull;
-    const int Dz = (int)p.shapes[3 * plan.level];
-    if (!((p.level_mask >> plan.level) & 1) || image_bytes <= p.l2_keep_bytes || Dz < 2) return plan;
-    unsigned long long want = (image_bytes + p.bin_slab_bytes - 1) / p.bin_slab_bytes;
+    const unsigned long long image_bytes = best * (unsigned long long)GD * 4ull;
+    const int Dz = (int)shapes[3 * plan.level];
+    if (!((level_mask >> plan.level) & 1) || image_bytes <= l2_keep_bytes || Dz < 2) return plan;
+    unsigned long long want = (image_bytes + slab_bytes - 1) / slab_bytes;
     if (want > (unsigned long long)kMaxSlabs) want = kMaxSlabs;
     if (want > (unsigned long long)Dz) want = Dz;
     if (want < 2) want = 2;
@@ -92,6 +96,9 @@ __device__ __forceinline__ BinPlan make_bin_plan(const Problem &p) {
     plan.slabs = (Dz + plan.depth - 1) / plan.depth;
     plan.enabled = 1;
     return plan;
+}
+__device__ __forceinline__ BinPlan make_bin_plan(const Problem &p) {
+    return bin_plan_from(p.shapes, p.L, p.GD, p.l2_keep_bytes, p.bin_slab_bytes, p.level_mask, p.bin_allowed);
 }
 
 // ---------------------------------------------------------------------------

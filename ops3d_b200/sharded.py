@@ -48,8 +48,10 @@ class PeerReducer:
     multicast back, when the buffers have a multicast binding; else ``fda_peer_reduce_cast``: pull my
     slice from all ranks, sum, cast, push to all ranks) -> barrier, while the caller's stream already scatters the next batch element.  Only the last
     batch element's exchange is exposed.  When ``spatial_shapes`` is given, each batch element is
-    further split into two launches -- the largest pyramid level first, the others second -- so that
-    the largest level's share of the image (most of the bytes) travels while the second launch runs.
+    further split: the largest pyramid level first, the others second, so that the largest level's
+    share of the image (most of the bytes) travels while the rest computes; and when that level is
+    handled by the slab-binned kernels, it is launched in slab groups whose finished z-ranges are
+    exchanged one by one (``FDA_SLAB_PARTS``, 4 by default).
 
     ``backward`` returns a ``grad_value`` that aliases the symmetric buffer: it is valid until the
     next ``backward`` call on this object (clone it to keep it longer).
@@ -94,6 +96,9 @@ class PeerReducer:
         # Level schedule: the largest level first (when it sits at either end of the pyramid), so that
         # its share of the image -- most of the bytes -- is exchanged while the other levels compute.
         self.passes = None
+        self.shapes_host = None if spatial_shapes is None else torch.as_tensor(spatial_shapes).cpu().long().contiguous()
+        self.slab_plan = None     # decided at the first backward (needs the query and point counts)
+        self.slab_plan_key = None
         if spatial_shapes is not None and os.environ.get("FDA_LEVEL_SPLIT", "1") != "0":
             cells = [int(c) for c in torch.as_tensor(spatial_shapes).cpu().prod(1).tolist()]
             L = len(cells)
@@ -109,6 +114,41 @@ class PeerReducer:
                     self.ranges = [(starts[a] * gd, starts[b] * gd) for a, b in self.passes]  # element ranges
                     if any((e0 % 8) or (e1 % 8) for e0, e1 in self.ranges):
                         self.passes = None
+
+    def _plan_slabs(self, value, packed, K, scratch):
+        """Host copy of the kernels' slab plan (same function, fda_backward_bin_plan) -> exchange ranges."""
+        import os
+
+        from . import capi
+
+        key = (packed.shape[1], K)
+        if self.slab_plan_key == key:
+            return
+        self.slab_plan_key, self.slab_plan = key, None
+        if self.shapes_host is None or scratch is None or os.environ.get("FDA_LEVEL_SPLIT", "1") == "0":
+            return
+        plan = capi.bin_plan(self.shapes_host, (1,) + tuple(value.shape[1:]), packed.shape[1], K)
+        if plan is None:
+            return
+        level, slabs, depth = plan
+        dims = [tuple(int(v) for v in row) for row in self.shapes_host.tolist()]
+        cells = [d * h * w for d, h, w in dims]
+        if sum(cells) != self.shape[1]:
+            return
+        gd = self.shape[2] * self.shape[3]
+        start = sum(cells[:level])
+        Dz, H, W = dims[level]
+        parts = max(1, min(int(os.environ.get("FDA_SLAB_PARTS", "4")), slabs))
+        part_ranges = []
+        for g in range(parts):
+            z0 = (slabs * g // parts) * depth
+            z1 = min((slabs * (g + 1) // parts) * depth, Dz)
+            part_ranges.append(((start + z0 * H * W) * gd, (start + z1 * H * W) * gd))
+        rest = [(0, start * gd), ((start + cells[level]) * gd, self.per_batch)]
+        rest_ranges = [(a, b) for a, b in rest if b > a]
+        if any((a % 8) or (b % 8) for a, b in part_ranges + rest_ranges):
+            return
+        self.slab_plan = (parts, part_ranges, rest_ranges)
 
     def _exchange(self, elem_begin, elem_count, out_elem):
         """barrier -> reduce+cast of image[elem_begin : elem_begin+elem_count) -> barrier, on the current stream."""
@@ -153,18 +193,36 @@ class PeerReducer:
 
         from . import capi as _capi
         if self.scratch is None:
+            # one scratch per batch element: in pass-major order the slab lists of every element stay alive
             nbytes = _capi.scratch_bytes(value[:1], packed[:1], K)
-            self.scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=self.device) if nbytes else False
-        scratch = self.scratch if self.scratch is not False else None
+            self.scratch = [torch.empty(nbytes, dtype=torch.uint8, device=self.device) for _ in range(B)] if nbytes else False
+        scratch_of = (lambda b: self.scratch[b]) if self.scratch is not False else (lambda b: None)
+        scratch = scratch_of(0)
+        self._plan_slabs(value, packed, K, scratch)
 
         def args_of(b):
             return (value[b:b + 1], shapes, lsi, packed[b:b + 1], grad_out[b:b + 1], K, self.image[b:b + 1],
                     grad_packed[b:b + 1])
 
-        if self.passes is None:
+        if self.slab_plan is not None:
+            # Slab pipeline: the largest level is scattered slab group by slab group; the z-range a group has
+            # finished is handed to the exchange while the next group (and later the other levels) compute.
+            parts, part_ranges, rest_ranges = self.slab_plan
+            for g in range(parts):
+                for b in range(B):
+                    capi.backward_binned_part(*args_of(b), g, parts, capi.BWD_ZERO_IMAGE, scratch_of(b), im2col_step=im2col_step)
+                    e0, e1 = part_ranges[g]
+                    hand_over(b * self.per_batch + e0, e1 - e0)
+            for b in range(B):
+                capi.backward_accumulate_levels(*args_of(b), 0, shapes.shape[0],
+                                                capi.BWD_RESUME | capi.BWD_FINALIZE | capi.BWD_BINNED_DONE,
+                                                im2col_step=im2col_step, scratch=scratch_of(b))
+                for e0, e1 in rest_ranges:
+                    hand_over(b * self.per_batch + e0, e1 - e0)
+        elif self.passes is None:
             for b in range(B):
                 capi.backward_accumulate_levels(*args_of(b), 0, shapes.shape[0], capi.BWD_ZERO_IMAGE | capi.BWD_FINALIZE,
-                                                im2col_step=im2col_step, scratch=scratch)
+                                                im2col_step=im2col_step, scratch=scratch_of(b))
                 hand_over(b * self.per_batch, self.per_batch)
         else:
             # pass-major order: the big level of every batch element first, so that all of its exchanges
@@ -173,7 +231,7 @@ class PeerReducer:
                 last = n == len(self.passes) - 1
                 flags = (capi.BWD_ZERO_IMAGE if n == 0 else capi.BWD_RESUME) | (capi.BWD_FINALIZE if last else 0)
                 for b in range(B):
-                    capi.backward_accumulate_levels(*args_of(b), lb, le, flags, im2col_step=im2col_step, scratch=scratch)
+                    capi.backward_accumulate_levels(*args_of(b), lb, le, flags, im2col_step=im2col_step, scratch=scratch_of(b))
                     hand_over(b * self.per_batch + e0, e1 - e0)
         main.wait_stream(self.side)
         return self.out, grad_packed

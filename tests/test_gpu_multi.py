@@ -34,7 +34,9 @@ def _free_port():
 def _worker(rank, world, port, mode, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
                       FDA_SHARDED_REDUCE="nccl" if mode == "nccl" else "peer",
-                      FDA_PEER_REDUCE_MODE="auto" if mode == "nccl" else mode)
+                      FDA_PEER_REDUCE_MODE="auto" if mode in ("nccl", "slab-pipeline") else mode)
+    if mode == "slab-pipeline":  # force the slab-binned backward and its slab-group exchange on this small problem
+        os.environ.update(FDA_L2_KEEP_FRACTION="0.00001", FDA_BIN_SLAB_MB="0.25", FDA_SLAB_PARTS="3")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -66,7 +68,7 @@ def _worker(rank, world, port, mode, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["p2p", "push", "multimem", "nccl"])
+@pytest.mark.parametrize("mode", ["p2p", "push", "multimem", "nccl", "slab-pipeline"])
 def test_two_gpus_sharded_equals_unsharded(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
