@@ -38,6 +38,36 @@ def shard_queries(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return t[:, b:e].contiguous()
 
 
+def slab_exchange_ranges(shapes_host, value_shape, plan, parts):
+    """Element ranges (inside one batch element's ``[N, G, D]`` image) that become final, in order, when the
+    largest level is scattered in ``parts`` slab groups and the other levels afterwards.
+
+    ``plan = (level, slabs, planes_per_slab)`` as returned by ``capi.bin_plan``.  Returns
+    ``(parts, part_ranges, rest_ranges)`` or ``None`` when a range would not be a multiple of 8 elements.
+    After slab group g the planes ``[first_slab*depth, min(end_slab*depth, D))`` of the level are final: a
+    slab's points touch planes z0 and z0+1, so the plane just above a group still receives the next slab."""
+    level, slabs, depth = plan
+    dims = [tuple(int(v) for v in row) for row in torch.as_tensor(shapes_host).tolist()]
+    cells = [d * h * w for d, h, w in dims]
+    if sum(cells) != value_shape[1]:
+        return None
+    gd = value_shape[2] * value_shape[3]
+    per_batch = value_shape[1] * gd
+    start = sum(cells[:level])
+    Dz, H, W = dims[level]
+    parts = max(1, min(parts, slabs))
+    part_ranges = []
+    for g in range(parts):
+        z0 = (slabs * g // parts) * depth
+        z1 = min((slabs * (g + 1) // parts) * depth, Dz)
+        part_ranges.append(((start + z0 * H * W) * gd, (start + z1 * H * W) * gd))
+    rest = [(0, start * gd), ((start + cells[level]) * gd, per_batch)]
+    rest_ranges = [(a, b) for a, b in rest if b > a]
+    if any((a % 8) or (b % 8) for a, b in part_ranges + rest_ranges):
+        return None
+    return parts, part_ranges, rest_ranges
+
+
 class PeerReducer:
     """Backward of one rank with the cross-GPU reduction fused into the cast and overlapped with compute.
 
@@ -130,25 +160,8 @@ class PeerReducer:
         plan = capi.bin_plan(self.shapes_host, (1,) + tuple(value.shape[1:]), packed.shape[1], K)
         if plan is None:
             return
-        level, slabs, depth = plan
-        dims = [tuple(int(v) for v in row) for row in self.shapes_host.tolist()]
-        cells = [d * h * w for d, h, w in dims]
-        if sum(cells) != self.shape[1]:
-            return
-        gd = self.shape[2] * self.shape[3]
-        start = sum(cells[:level])
-        Dz, H, W = dims[level]
-        parts = max(1, min(int(os.environ.get("FDA_SLAB_PARTS", "4")), slabs))
-        part_ranges = []
-        for g in range(parts):
-            z0 = (slabs * g // parts) * depth
-            z1 = min((slabs * (g + 1) // parts) * depth, Dz)
-            part_ranges.append(((start + z0 * H * W) * gd, (start + z1 * H * W) * gd))
-        rest = [(0, start * gd), ((start + cells[level]) * gd, self.per_batch)]
-        rest_ranges = [(a, b) for a, b in rest if b > a]
-        if any((a % 8) or (b % 8) for a, b in part_ranges + rest_ranges):
-            return
-        self.slab_plan = (parts, part_ranges, rest_ranges)
+        parts = max(1, int(os.environ.get("FDA_SLAB_PARTS", "4")))
+        self.slab_plan = slab_exchange_ranges(self.shapes_host, self.shape, plan, parts)
 
     def _exchange(self, elem_begin, elem_count, out_elem):
         """barrier -> reduce+cast of image[elem_begin : elem_begin+elem_count) -> barrier, on the current stream."""

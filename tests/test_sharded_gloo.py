@@ -71,3 +71,28 @@ def test_two_ranks_reproduce_the_unsharded_result():
     ret = mp.get_context("spawn").Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def test_slab_plan_and_exchange_ranges_tile_the_image():
+    """Host-side slab plan (the C function the kernels share) and the exchange ranges derived from it."""
+    from ops3d_b200 import capi
+    from ops3d_b200.sharded import slab_exchange_ranges
+
+    shapes = torch.tensor([(32, 64, 256), (16, 32, 128), (8, 16, 64)])
+    N, G, D = int(shapes.prod(1).sum()), 8, 32
+    plan = capi.bin_plan(shapes, (1, N, G, D), 74752, 8)
+    assert plan == (0, 32, 1)  # level 0 in 32 slabs of one plane: 16.8 MB of image each (target 16 MB)
+    assert capi.bin_plan(torch.tensor([(4, 8, 8), (2, 4, 4)]), (1, 288, 4, 16), 288, 4) is None  # fits L2: no binning
+    for level_first in (True, False):
+        sh = shapes if level_first else shapes.flip(0)
+        pl = capi.bin_plan(sh, (1, N, G, D), 1000, 8)
+        for parts in (1, 3, 4, 32, 40):
+            got = slab_exchange_ranges(sh, (1, N, G, D), pl, parts)
+            assert got is not None
+            n, part_ranges, rest_ranges = got
+            assert n == min(parts, 32) and len(part_ranges) == n
+            ranges = sorted(part_ranges + rest_ranges)
+            assert ranges[0][0] == 0 and ranges[-1][1] == N * G * D
+            for (a, b), (c, d) in zip(ranges, ranges[1:]):
+                assert b == c and a < b  # contiguous, no gap, no overlap
+            assert all(b > a for a, b in part_ranges)
