@@ -120,7 +120,11 @@ class PeerReducer:
             self.staging = symm_mem.empty(self.world * self.slot, dtype=torch.float32, device=device)
             self.h_staging = symm_mem.rendezvous(self.staging, self.group)
             self.staging_ptrs = [int(p) for p in self.h_staging.buffer_ptrs]
-        self.scratch = None  # slab-binning scratch for one batch element, allocated on first use
+        self.scratch = None  # slab-binning scratch per batch element, allocated on first use
+        # The image is handed back zero-filled after every backward (on the side stream, off the critical
+        # path: it overlaps whatever the caller runs next), so the scatter kernels need not clear it first.
+        self.image.zero_()
+        self._image_clean = True
         if self.per_batch % 8:
             raise ValueError("elements per batch element must be a multiple of 8")
         # Level schedule: the largest level first (when it sits at either end of the pyramid), so that
@@ -195,6 +199,9 @@ class PeerReducer:
             grad_packed = torch.empty_like(packed)
         main = torch.cuda.current_stream(self.device)
         self.side.wait_stream(main)  # earlier readers of self.out / self.image are done
+        main.wait_stream(self.side)  # the zero-fill issued after the previous backward is done
+        zero = 0 if self._image_clean else capi.BWD_ZERO_IMAGE
+        self._image_clean = False
         out_elem = self.out.element_size()
 
         def hand_over(elem_begin, elem_count):
@@ -223,7 +230,7 @@ class PeerReducer:
             parts, part_ranges, rest_ranges = self.slab_plan
             for g in range(parts):
                 for b in range(B):
-                    capi.backward_binned_part(*args_of(b), g, parts, capi.BWD_ZERO_IMAGE, scratch_of(b), im2col_step=im2col_step)
+                    capi.backward_binned_part(*args_of(b), g, parts, zero, scratch_of(b), im2col_step=im2col_step)
                     e0, e1 = part_ranges[g]
                     hand_over(b * self.per_batch + e0, e1 - e0)
             for b in range(B):
@@ -234,7 +241,7 @@ class PeerReducer:
                     hand_over(b * self.per_batch + e0, e1 - e0)
         elif self.passes is None:
             for b in range(B):
-                capi.backward_accumulate_levels(*args_of(b), 0, shapes.shape[0], capi.BWD_ZERO_IMAGE | capi.BWD_FINALIZE,
+                capi.backward_accumulate_levels(*args_of(b), 0, shapes.shape[0], zero | capi.BWD_FINALIZE,
                                                 im2col_step=im2col_step, scratch=scratch_of(b))
                 hand_over(b * self.per_batch, self.per_batch)
         else:
@@ -242,11 +249,16 @@ class PeerReducer:
             # hide behind later launches and only the small remainder of the last element is exposed
             for n, ((lb, le), (e0, e1)) in enumerate(zip(self.passes, self.ranges)):
                 last = n == len(self.passes) - 1
-                flags = (capi.BWD_ZERO_IMAGE if n == 0 else capi.BWD_RESUME) | (capi.BWD_FINALIZE if last else 0)
+                flags = (zero if n == 0 else capi.BWD_RESUME) | (capi.BWD_FINALIZE if last else 0)
                 for b in range(B):
                     capi.backward_accumulate_levels(*args_of(b), lb, le, flags, im2col_step=im2col_step, scratch=scratch_of(b))
                     hand_over(b * self.per_batch + e0, e1 - e0)
-        main.wait_stream(self.side)
+        finished = torch.cuda.Event()
+        finished.record(self.side)
+        main.wait_event(finished)       # all exchanges done: self.out is complete on every rank
+        with torch.cuda.stream(self.side):
+            self.image.zero_()          # every rank has finished reading this image (last barrier above)
+        self._image_clean = True
         return self.out, grad_packed
 
 
