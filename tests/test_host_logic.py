@@ -59,3 +59,33 @@ def test_cpu_tensors_raise_instead_of_falling_back():
     value, shapes, lsi, packed = _cpu_inputs()
     with pytest.raises((RuntimeError, AssertionError)):
         FlashDeformAttnFunction.apply(value, shapes, lsi, packed, 1, 4, True)
+
+
+def test_product_package_never_touches_the_oracle():
+    """The oracle is test infrastructure: nothing under ops3d_b200/ (Python or C++/CUDA) may import,
+    include, load or call it, and the package has no CPU code path to fall back to."""
+    import os
+    import re
+
+    root = os.path.dirname(os.path.abspath(ops3d_b200.__file__))
+    offenders = []
+    for dirpath, _, files in os.walk(root):
+        for name in files:
+            if not name.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                continue
+            text = open(os.path.join(dirpath, name), encoding="utf-8").read()
+            pattern = r"\b(import|from)\s+oracle\b|oracle/|fda_oracle|libfda_oracle"
+            if name.endswith(".py"):
+                pattern += r"|grid_sample\("  # no PyTorch re-implementation of the operator inside the package
+            if re.search(pattern, text):
+                offenders.append(os.path.relpath(os.path.join(dirpath, name), root))
+    assert offenders == []
+
+
+def test_operator_fails_loudly_without_the_extension(monkeypatch):
+    import ops3d_b200.flash_deform_attn as mod
+
+    monkeypatch.setattr(mod, "_C", None)
+    value, shapes, lsi, packed = _cpu_inputs()
+    with pytest.raises(RuntimeError, match="extension not built"):
+        FlashDeformAttnFunction.apply(value, shapes, lsi, packed, 1, 4, True)
