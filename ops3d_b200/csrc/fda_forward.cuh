@@ -18,7 +18,7 @@
 #include "fda_device.cuh"
 
 #ifndef FDA_FWD_MIN_BLOCKS
-#define FDA_FWD_MIN_BLOCKS 2
+#define FDA_FWD_MIN_BLOCKS 3
 #endif
 
 namespace fda {
