@@ -236,6 +236,17 @@ int fda_multimem_reduce_cast(const float *mc_image, void *mc_output, int world, 
                              size_t num_elements, int value_dtype, void *stream);
 
 /*
+ * Builds the operator's planar input from what a multi-scale deformable-attention layer has after
+ * its projections: offsets [B,Lq,G,L,K,3] (x,y,z, in cells of level l), reference_points [B,Lq,L,3]
+ * (normalised), logits [B,Lq,G,L,K], all of `dtype`; packed [B,Lq,G,L*K*4] is fp32:
+ * coordinates reference + offset / (W_l,H_l,D_l), then the logits.  One fused pass.  The reference
+ * leaves this step to its callers (its tests build the tensor with torch.cat).
+ */
+int fda_pack_sampling(const void *offsets, const void *reference_points, const void *logits,
+                      const int64_t *spatial_shapes, float *packed, int batch, int num_query, int num_heads,
+                      int num_levels, int num_points, int dtype, void *stream);
+
+/*
  * Backward pass that needs no workspace from the caller and allocates nothing: same inputs,
  * outputs and results as fda_backward, but the fp32 accumulation image sits in a fixed
  * FDA_NOALLOC_MAX_ELEMENTS-float (64 MiB) array inside the library, present on every GPU that

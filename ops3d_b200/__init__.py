@@ -8,3 +8,4 @@ from ._extension import _C
 from .flash_deform_attn import FlashDeformAttnFunction, findspec, findspec_bwd
 
 __all__ = ["FlashDeformAttnFunction", "findspec", "findspec_bwd", "_C"]
+# The layer around the operator lives in ops3d_b200.msda3d (MSDeformAttn3D); imported on demand.

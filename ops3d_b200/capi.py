@@ -19,6 +19,7 @@ EXPORTS = (
     "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
     "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
+    "fda_pack_sampling",
 )
 BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE = 1, 2, 4, 8
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
@@ -70,6 +71,8 @@ def load() -> ctypes.CDLL:
     lib.fda_backward_bin_plan.restype = i
     lib.fda_backward_binned_part.argtypes = [vp] * 7 + [i] * 13 + [vp, sz, vp]
     lib.fda_backward_binned_part.restype = i
+    lib.fda_pack_sampling.argtypes = [vp] * 5 + [i] * 6 + [vp]
+    lib.fda_pack_sampling.restype = i
     lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
     lib.fda_cast_grad_value.restype = i
     lib.fda_backward_noalloc.argtypes = [vp] * 7 + [i] * 10 + [vp]
@@ -270,3 +273,15 @@ def peer_reduce_staged_cast(image_ptr, staging_ptr, slot_stride, output_ptrs, ra
         check(load().fda_peer_reduce_staged_cast(image_ptr, staging_ptr, slot_stride, outs, world, rank, num_elements,
                                                  DTYPE_CODE[dtype], torch.cuda.current_stream(device).cuda_stream))
     _count(1)
+
+
+def pack_sampling(offsets, reference_points, logits, shapes):
+    """``fda_pack_sampling``: offsets ``[B,Q,G,L,K,3]``, reference points ``[B,Q,L,3]``, logits ``[B,Q,G,L,K]``
+    (one dtype, contiguous, CUDA) -> packed ``[B,Q,G,L*K*4]`` fp32."""
+    B, Q, G, L, K, _ = offsets.shape
+    packed = torch.empty(B, Q, G, L * K * 4, dtype=torch.float32, device=offsets.device)
+    with torch.cuda.device(offsets.device):
+        check(load().fda_pack_sampling(offsets.data_ptr(), reference_points.data_ptr(), logits.data_ptr(), shapes.data_ptr(),
+                                       packed.data_ptr(), B, Q, G, L, K, DTYPE_CODE[offsets.dtype], _stream(offsets)))
+    _count(1)
+    return packed
