@@ -69,3 +69,42 @@ def test_backward_workspace_contract():
     assert lib.fda_backward(p, p, p, p, p, p, p, None, 0, *args) == 8        # workspace missing
     assert lib.fda_backward(p, p, p, p, p, p, p, p, 16, *args) == 8          # workspace too small
     assert lib.fda_backward(p, p, p, p, p, None, p, p, 1 << 20, *args) == 1  # null output
+
+
+def test_level_range_and_slab_part_validation():
+    lib = capi.load()
+    p = ctypes.c_void_p(256)
+    dims = (1, 8, 1, 8, 2, 1, 4, 2, 0, 64)  # B, N, G, D, L, Q, K, value bf16, packed f32, im2col_step
+    # empty / reversed / out-of-range level ranges
+    for lb, le in ((1, 1), (2, 1), (0, 3), (-1, 1)):
+        assert lib.fda_backward_accumulate_levels(p, p, p, p, p, p, p, *dims, lb, le, 5, None, 0, None) == 3
+    # slab-part launches need scratch and a problem whose image exceeds L2
+    assert lib.fda_backward_binned_part(p, p, p, p, p, p, p, *dims, 0, 4, 1, None, 0, None) == 8
+    assert lib.fda_backward_binned_part(p, p, p, p, p, p, p, *dims, 4, 4, 1, p, 1 << 30, None) == 6  # part >= parts
+    # BINNED_DONE without usable scratch is a caller error, not a silent full recomputation
+    assert lib.fda_backward_accumulate_levels(p, p, p, p, p, p, p, *dims, 0, 2, 2 | 4 | 8, None, 0, None) == 8
+
+
+def test_exchange_kernels_validate_before_launch():
+    lib = capi.load()
+    ptrs = (ctypes.c_void_p * 2)(256, 512)
+    assert lib.fda_peer_reduce_cast(None, ptrs, 2, 0, 64, 2, None) == 1
+    assert lib.fda_peer_reduce_cast(ptrs, ptrs, 2, 2, 64, 2, None) == 6      # rank outside world
+    assert lib.fda_peer_reduce_cast(ptrs, ptrs, 2, 0, 60, 2, None) == 6      # not a multiple of 8 elements
+    assert lib.fda_peer_reduce_cast(ptrs, ptrs, 17, 0, 64, 2, None) == 6     # more than 16 ranks
+    bad = (ctypes.c_void_p * 2)(256, 520)
+    assert lib.fda_peer_reduce_cast(bad, ptrs, 2, 0, 64, 2, None) == 9       # misaligned peer buffer
+    assert lib.fda_multimem_reduce_cast(None, ctypes.c_void_p(256), 2, 0, 64, 2, None) == 1
+    assert lib.fda_peer_push_partials(ctypes.c_void_p(256), ptrs, 16, 2, 0, 64, None) == 6  # slot shorter than a slice
+    assert lib.fda_pack_sampling(None, None, None, None, None, 1, 1, 1, 1, 4, 0, None) == 1
+    assert lib.fda_pack_sampling(ctypes.c_void_p(256), ctypes.c_void_p(256), ctypes.c_void_p(256), ctypes.c_void_p(256),
+                                 ctypes.c_void_p(256), 1, 1, 1, 6, 4, 0, None) == 3
+
+
+def test_bin_plan_is_a_pure_host_function():
+    import torch
+
+    shapes = torch.tensor([(32, 64, 256), (16, 32, 128), (8, 16, 64)])
+    assert capi.bin_plan(shapes, (2, 598016, 8, 32), 598016, 8) == (0, 32, 1)
+    assert capi.bin_plan(shapes.flip(0), (1, 598016, 8, 32), 1000, 4) == (2, 32, 1)   # largest level last
+    assert capi.bin_plan(torch.tensor([(16, 32, 128), (8, 16, 64)]), (1, 73728, 8, 32), 73728, 4) is None  # 75 MB image fits
