@@ -149,6 +149,23 @@ class PeerReducer:
                     if any((e0 % 8) or (e1 % 8) for e0, e1 in self.ranges):
                         self.passes = None
 
+    def _check_level_order(self, lsi):
+        """The level-wise and slab-wise exchange ranges assume levels stored back to back in index order
+        (level_start_index = exclusive cumsum of the level sizes).  Checked once per level_start_index
+        tensor; any other arrangement falls back to one exchange per batch element."""
+        key = (lsi.data_ptr(), lsi._version)
+        if getattr(self, "_lsi_checked", None) == key:
+            return
+        self._lsi_checked = key
+        if self.shapes_host is None:
+            return
+        cells = self.shapes_host.prod(1)
+        standard = torch.cat((cells.new_zeros(1), cells.cumsum(0)[:-1]))
+        if not torch.equal(lsi.detach().cpu().long(), standard):
+            self.shapes_host = None   # disables both split pipelines
+            self.passes = None
+            self.slab_plan, self.slab_plan_key = None, None
+
     def _plan_slabs(self, value, packed, K, scratch):
         """Host copy of the kernels' slab plan (same function, fda_backward_bin_plan) -> exchange ranges."""
         import os
@@ -222,6 +239,7 @@ class PeerReducer:
             self.scratch = [torch.empty(nbytes, dtype=torch.uint8, device=self.device) for _ in range(B)] if nbytes else False
         scratch_of = (lambda b: self.scratch[b]) if self.scratch is not False else (lambda b: None)
         scratch = scratch_of(0)
+        self._check_level_order(lsi)
         self._plan_slabs(value, packed, K, scratch)
 
         def args_of(b):
