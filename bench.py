@@ -325,7 +325,21 @@ def run_ours(args, cfg):
     grad_value = torch.empty_like(value)
     grad_packed = torch.empty_like(packed)
     use_peer = world > 1 and args.reduce == "peer"
-    reducer = PeerReducer(value.shape, vdt, dev, spatial_shapes=shapes) if use_peer else None
+    reducer, peer_note = None, None
+    if use_peer:
+        # symmetric-memory set-up can be unavailable on a machine (no peer access): all ranks agree, then
+        # either all use the fused exchange or all fall back to NCCL all-reduce + cast
+        try:
+            reducer = PeerReducer(value.shape, vdt, dev, spatial_shapes=shapes)
+            ok = torch.ones(1, device=dev)
+        except Exception as exc:  # noqa: BLE001
+            peer_note = f"peer exchange unavailable ({type(exc).__name__}: {exc}); NCCL all-reduce used"
+            ok = torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            reducer, use_peer = None, False
+            os.environ["FDA_SHARDED_REDUCE"] = "nccl"  # the end-to-end leg follows suit
+            peer_note = peer_note or "peer exchange unavailable on another rank; NCCL all-reduce used"
     reducer_passes = reducer.passes if use_peer else None
     L = len(cfg["shapes"])
     n_scratch = capi.scratch_bytes(value, packed, K)
@@ -464,7 +478,8 @@ def run_ours(args, cfg):
                        "sharding": (f"queries/{world}, value replicated, grad_value fp32 images summed by "
                                     + ("a fused peer-memory reduce+cast kernel overlapped per batch element" if use_peer
                                        else "NCCL all-reduce, then cast")) if world > 1 else "none",
-                       "l2": "inputs larger than L2 (no flush needed)" if bm["fwd_bwd"] > 4e8 else "inputs smaller than L2"},
+                       "l2": "inputs larger than L2 (no flush needed)" if bm["fwd_bwd"] > 4e8 else "inputs smaller than L2",
+                       **({"note": peer_note} if peer_note else {})},
             "roofline": roofline,
             "e2e": {"value": (B / (e2e_ms * 1e-3)) if e2e_ms else None, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
