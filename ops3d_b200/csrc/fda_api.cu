@@ -223,7 +223,10 @@ int launch_bin_prepare(const fda::Problem &p, cudaStream_t st) {
 template <typename VT, typename PT>
 int launch_binned_slabs(const fda::Problem &p, cudaStream_t st) {
     // x: blocks striding over one slab's list; y: slab (slabs run one after the other); z: batch element
-    const dim3 grid(592, fda::kMaxSlabs, (unsigned)p.B);
+    int gx = 592;  // 4 blocks per SM's worth of 2 resident blocks: each block strides over its slab's list
+    if (const char *e = std::getenv("FDA_BIN_GRID_X")) gx = std::atoi(e);
+    if (gx < 1) gx = 1;
+    const dim3 grid((unsigned)gx, fda::kMaxSlabs, (unsigned)p.B);
     if (pair_rows<VT>(p)) fda::fda_backward_binned_kernel<VT, PT, true><<<grid, fda::kThreads, 0, st>>>(p);
     else fda::fda_backward_binned_kernel<VT, PT, false><<<grid, fda::kThreads, 0, st>>>(p);
     const cudaError_t e = cudaGetLastError();
