@@ -172,8 +172,7 @@ size_t bin_scratch_bytes(int B, int N, int G, int D, int Q, int K) {
     return round256((size_t)3 * B * fda::kMaxSlabs * sizeof(unsigned int)) + (size_t)B * cap * sizeof(uint2);
 }
 
-// Rows of exactly four lanes with two 16-byte reductions per lane (D = 32, 16-bit value): neighbouring
-// rows scatter as a team so that every reduction request covers a whole 128-byte line of the image.
+// Target size of one slab's share of the fp32 image (FDA_BIN_SLAB_MB overrides).
 unsigned long long bin_slab_bytes_setting() {
     double slab_mb = 16.0;  // share of the fp32 image per slab (value rows of the slab add half of that); 8-16 MB measured best on B200
     if (const char *e = std::getenv("FDA_BIN_SLAB_MB")) slab_mb = std::atof(e);
@@ -193,6 +192,8 @@ void attach_bin_scratch(fda::Problem &p, const Shape &s, void *scratch, size_t s
     p.bin_slab_bytes = bin_slab_bytes_setting();
 }
 
+// Rows of exactly four lanes with two 16-byte reductions per lane (D = 32, 16-bit value): neighbouring
+// rows scatter as a team so that every reduction request covers a whole 128-byte line of the image.
 template <typename VT>
 bool pair_rows(const fda::Problem &p) {
     if (const char *e = std::getenv("FDA_PAIR_ROWS")) if (std::atoi(e) == 0) return false;
