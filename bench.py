@@ -11,16 +11,21 @@ N=Lq=598016, G=8, D=32, K=8, bf16 value, fp32 offsets/logits).  A "sample" is on
 Rank 0 prints ONE JSON line.
 
   value        B / (device time of one step), inputs resident in HBM, C-ABI calls, CUDA events,
-               max over ranks.  With N > 1 GPUs the queries of every batch element are split over
-               the ranks, value is replicated and the fp32 grad_value images are all-reduced
-               (NCCL) before the cast -- total work is fixed, so scaling is "strong".
-  e2e          same metric through the public autograd API with HOST (pinned) inputs: every step
-               copies its inputs host->device and all results (out, grad_value, grad_packed)
-               device->host inside the timed region.
-  roofline     dominant kernel (backward scatter/gather): algorithmic bytes / CUDA-event time of
-               that launch against the measured HBM copy bandwidth.
+               max over ranks.  With N > 1 GPUs the (batch, query) rows are split over the ranks in
+               batch-aligned ranges, value is replicated and the partial fp32 grad_value images are
+               summed over NVLink before the cast -- total work is fixed, so scaling is "strong".
+  e2e          same metric with HOST (pinned) inputs and outputs through the package's host-buffer
+               entry point (ops3d_b200.host_stream): every step copies its inputs host->device and
+               all results (out, grad_value, grad_packed) device->host inside the timed region,
+               query chunk by query chunk, overlapped with the kernels.
+  roofline     dominant kernels (backward scatter/gather): algorithmic bytes (gather model: rows
+               gathered or scattered x row bytes) / CUDA-event time against the measured HBM copy
+               bandwidth; the DRAM bytes an ncu capture measured are reported beside it.
   cpu_baseline the CPU oracle (PyTorch restatement of the reference's CPU implementation) timed on
-               this machine's host cores on a bounded sample of the same workload (N=1 only).
+               this machine's host cores on a bounded sample of the same workload (N=1 only); the
+               same pass is compared with the GPU results of those rows ("parity").
+  parity       N=1: GPU vs CPU oracle on the sampled rows; N>1: sharded result vs an unsharded
+               recomputation on one GPU (all ranks agree on the verdict).  Outside the timed region.
 
 --impl reference times only that CPU implementation (rank 0; other ranks exit).
 """
@@ -55,38 +60,65 @@ CONFIGS = {
 }
 METRIC = "fwd+bwd samples/s (fwd samples/s and achieved GB/s vs HBM roofline beside it)"
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per full-size launch of the backward kernels of
-# config 5, from the ncu captures summarised under profiles/: measured on the reduced case
-# (--batch 1 --queries 74752, 1/16 of the rows over the same per-batch-element volume) and scaled x16.
-NCU_BACKWARD_TRAFFIC_BYTES = {5: 16 * (3.16e9 + 3.09e9)}
+CPU_SAMPLE_QUERIES = 65536  # fixed sample of the CPU arm: queries of one batch element against the full-size volume
+
+
+def kernel_fingerprint():
+    """Hash of the kernel sources: ties the DRAM-traffic figures in profiles/traffic.json to the code they
+    were captured from."""
+    import hashlib
+
+    h = hashlib.sha256()
+    csrc = os.path.join(ROOT, "ops3d_b200", "csrc")
+    for name in sorted(os.listdir(csrc)):
+        if name.startswith(("fda_backward", "fda_device", "fda_forward")):
+            h.update(open(os.path.join(csrc, name), "rb").read())
+    return h.hexdigest()[:16]
+
+
+def measured_traffic(config_id):
+    """DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per full-size backward of the configuration,
+    from the ncu capture recorded in profiles/traffic.json -- None when there is none or when the kernel
+    sources changed since it was taken."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(path):
+        return None, "no capture recorded"
+    rec = json.load(open(path))
+    entry = rec.get("configs", {}).get(str(config_id))
+    if entry is None:
+        return None, "no capture for this configuration"
+    if rec.get("kernel_fingerprint") != kernel_fingerprint():
+        return None, "kernel sources changed since the capture in profiles/traffic.json"
+    return float(entry["backward_dram_bytes_per_launch"]), entry.get("how", "")
 
 
 # ---------------------------------------------------------------------------------------------
 # synthetic inputs
 # ---------------------------------------------------------------------------------------------
-def make_device_inputs(cfg, dev, q_begin, q_end, seed=0):
+def make_device_inputs(cfg, dev, part, seed=0):
     """Seeded inputs of the configuration's shapes and distributions, generated on the device.
-    Every rank generates the same full ``value`` (replicated) and its own query range."""
+    Every rank generates the same full ``value`` (replicated) and the rows of its own partition
+    ``[part.b_begin:part.b_end, part.q_begin:part.q_end]``."""
     vdt = getattr(torch, cfg["vdt"])
     shapes = torch.tensor(cfg["shapes"], dtype=torch.long, device=dev)
     sizes = shapes.prod(1)
     lsi = torch.cat((sizes.new_zeros(1), sizes.cumsum(0)[:-1]))
     N = int(sizes.sum())
     B, G, D, K, L = cfg["B"], cfg["G"], cfg["D"], cfg["K"], len(cfg["shapes"])
-    Qr = q_end - q_begin
+    nb, Qr = part.b_end - part.b_begin, part.q_end - part.q_begin
     gen = torch.Generator(device=dev).manual_seed(seed)
     value = torch.randn(B, N, G, D, generator=gen, device=dev, dtype=torch.float32).to(vdt)
-    gen_q = torch.Generator(device=dev).manual_seed(seed * 1000 + 17 + q_begin)
-    packed = torch.empty(B, Qr, G, L * K * 4, device=dev, dtype=torch.float32)
+    gen_q = torch.Generator(device=dev).manual_seed(seed * 1000 + 17 + part.q_begin + 7919 * part.b_begin)
+    packed = torch.empty(nb, Qr, G, L * K * 4, device=dev, dtype=torch.float32)
     loc = packed[..., : L * K * 3]
     if cfg["coords"] == "uniform":
-        loc.copy_(torch.rand(B, Qr, G, L * K * 3, generator=gen_q, device=dev) * 1.1 - 0.05)
+        loc.copy_(torch.rand(nb, Qr, G, L * K * 3, generator=gen_q, device=dev) * 1.1 - 0.05)
     else:
-        centre = torch.rand(B, Qr, 1, 1, 3, generator=gen_q, device=dev)
-        pts = centre + 0.05 * torch.randn(B, Qr, G, L * K, 3, generator=gen_q, device=dev)
-        loc.copy_(pts.clamp_(-0.05, 1.05).reshape(B, Qr, G, L * K * 3))
-    packed[..., L * K * 3:].copy_(torch.randn(B, Qr, G, L * K, generator=gen_q, device=dev))
-    grad_out = torch.randn(B, Qr, G * D, generator=gen_q, device=dev, dtype=torch.float32).to(vdt)
+        centre = torch.rand(nb, Qr, 1, 1, 3, generator=gen_q, device=dev)
+        pts = centre + 0.05 * torch.randn(nb, Qr, G, L * K, 3, generator=gen_q, device=dev)
+        loc.copy_(pts.clamp_(-0.05, 1.05).reshape(nb, Qr, G, L * K * 3))
+    packed[..., L * K * 3:].copy_(torch.randn(nb, Qr, G, L * K, generator=gen_q, device=dev))
+    grad_out = torch.randn(nb, Qr, G * D, generator=gen_q, device=dev, dtype=torch.float32).to(vdt)
     return value, shapes, lsi, packed, grad_out
 
 
@@ -177,9 +209,20 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU baseline / reference arm: the CPU oracle on host cores, bounded sample
+# CPU baseline / reference arm: the CPU oracle on host cores, fixed bounded sample
 # ---------------------------------------------------------------------------------------------
-def cpu_reference_step_inputs(cfg, sample_q, seed=0):
+def config_block(cfg):
+    """The workload description; identical in both arms."""
+    N = sum(d * h * w for d, h, w in cfg["shapes"])
+    return {"workload": cfg["name"], "B": cfg["B"], "Lq": cfg["Q"], "N": N, "G": cfg["G"], "D": cfg["D"], "K": cfg["K"],
+            "levels": [list(s) for s in cfg["shapes"]],
+            "value_dtype": cfg["vdt"], "offsets_dtype": "float32",
+            "l2": "inputs larger than L2 (no flush between iterations)" if cfg["B"] * cfg["Q"] * cfg["G"] * len(cfg["shapes"]) * cfg["K"] * 16 > 2.6e8
+                  else "inputs smaller than L2 (warm numbers; latency configuration)"}
+
+
+def cpu_sample_inputs(cfg, sample_q, seed=0):
+    """Inputs of the CPU arm when it runs alone: one batch element, ``sample_q`` queries, full-size volume."""
     from oracle import fda_oracle
 
     value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(
@@ -190,46 +233,33 @@ def cpu_reference_step_inputs(cfg, sample_q, seed=0):
     return value, sh, packed, grad_out
 
 
-def cpu_reference_time(cfg, sample_q, steps, warmup):
-    """Seconds per pass (fwd, fwd+bwd) of the CPU oracle over ``sample_q`` queries of ONE batch element
-    with the full-size value volume, all host threads."""
+def cpu_reference_pass(value, sh, packed, grad_out, K, steps, warmup):
+    """Best seconds per pass (fwd, fwd+bwd) of the CPU oracle on all host threads, after ``warmup`` untimed
+    passes; also returns the results of the last fwd+bwd pass (used as the parity check's reference)."""
     from oracle import fda_oracle
 
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    value, sh, packed, grad_out = cpu_reference_step_inputs(cfg, sample_q)
-    K = cfg["K"]
-    t_f, t_fb = [], []
+    t_f, t_fb, res = [], [], None
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        fda_oracle.fused_forward(value, sh, packed, K, chunk=sample_q)
+        fda_oracle.fused_forward(value, sh, packed, K, chunk=packed.shape[1])
         t1 = time.perf_counter()
-        fda_oracle.fused_forward_backward(value, sh, packed, grad_out, K, chunk=sample_q)
+        res = fda_oracle.fused_forward_backward(value, sh, packed, grad_out, K, chunk=packed.shape[1])
         t2 = time.perf_counter()
         if i >= warmup:
             t_f.append(t1 - t0)
             t_fb.append(t2 - t1)
-    return min(t_f), min(t_fb), cores
+    return min(t_f), min(t_fb), cores, res
 
 
-def pick_cpu_sample(cfg, budget_s):
-    """Largest power-of-two query count whose forward+backward is expected to fit ``budget_s``."""
-    q = min(cfg["Q"], 1024)
-    tf, tfb, _ = cpu_reference_time(cfg, q, 1, 0)
-    while q * 2 <= cfg["Q"] and (tf + tfb) * 2.2 < budget_s and q < 65536:
-        q *= 2
-        tf, tfb, _ = cpu_reference_time(cfg, q, 1, 0)
-    return q
-
-
-def cpu_baseline_block(cfg, steps=1, warmup=0, budget_s=6.0):
-    q = pick_cpu_sample(cfg, budget_s)
-    tf, tfb, cores = cpu_reference_time(cfg, q, steps, warmup)
-    scale = q / cfg["Q"]  # fraction of one sample (= one batch element) the pass covered
+def cpu_block(cfg, sample_q, tf, tfb, cores):
+    scale = sample_q / cfg["Q"]  # fraction of one sample (= one batch element) a pass covered
     return {
         "value": scale / tfb, "fwd_value": scale / tf, "unit": "samples/s", "cores": cores, "kind": "port",
-        "sample": f"{q} of {cfg['Q']} queries of one batch element against the full-size value volume, fp32, "
-                  f"torch {torch.__version__} CPU, linear extrapolation to a whole sample; fwd+bwd {tfb:.3f} s, fwd {tf:.3f} s",
+        "sample": f"{sample_q} of {cfg['Q']} queries of one batch element against the full-size value volume, fp32, "
+                  f"torch {torch.__version__} CPU, one untimed warm-up pass, linear extrapolation to a whole sample; "
+                  f"fwd+bwd {tfb:.3f} s, fwd {tf:.3f} s",
     }
 
 
@@ -237,14 +267,15 @@ def run_reference_arm(args, cfg):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    block = cpu_baseline_block(cfg, steps=max(1, args.steps), warmup=max(0, args.warmup), budget_s=8.0)
+    sample_q = min(cfg["Q"], CPU_SAMPLE_QUERIES)
+    value, sh, packed, grad_out = cpu_sample_inputs(cfg, sample_q)
+    tf, tfb, cores, _ = cpu_reference_pass(value, sh, packed, grad_out, cfg["K"], max(1, args.steps), max(1, args.warmup))
+    block = cpu_block(cfg, sample_q, tf, tfb, cores)
     line = {
         "impl": "reference", "metric": METRIC, "value": block["value"], "fwd_value": block["fwd_value"],
         "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": None, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg["name"], "B": cfg["B"], "Lq": cfg["Q"], "G": cfg["G"], "D": cfg["D"], "K": cfg["K"],
-                   "levels": cfg["shapes"]},
+        "ms_per_step": cfg["B"] / block["value"] * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": config_block(cfg),
         "cpu_baseline": block,
         "e2e": {"value": block["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -253,7 +284,7 @@ def run_reference_arm(args, cfg):
 
 
 # ---------------------------------------------------------------------------------------------
-# optional: the reference's own CUDA kernels on this GPU (reported baseline; needs baseline/_ref/)
+# the reference's own CUDA kernels on this GPU (reported baseline; needs baseline/_ref/)
 # ---------------------------------------------------------------------------------------------
 def reference_cuda_block(cfg, value, shapes, lsi, packed, grad_out, steps=5, warmup=2):
     """Times the unmodified reference kernels (built by baseline/build_ref_cuda.sh) on the same inputs.
@@ -263,12 +294,15 @@ def reference_cuda_block(cfg, value, shapes, lsi, packed, grad_out, steps=5, war
     so = os.path.join(ROOT, "baseline", "_ref", "ops3d_ref_C.so")
     if not os.path.exists(so):
         return {"unavailable": "baseline/_ref/ops3d_ref_C.so not built (baseline/build_ref_cuda.sh <reference checkout>)"}
-    spec = importlib.util.spec_from_file_location("ops3d_ref_C", so)
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
+    try:
+        spec = importlib.util.spec_from_file_location("ops3d_ref_C", so)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    except Exception as exc:  # noqa: BLE001  (built for another torch / python)
+        return {"unavailable": f"baseline/_ref/ops3d_ref_C.so does not load: {type(exc).__name__}: {exc}"}
     B, Q, G, D, K = cfg["B"], packed.shape[1], cfg["G"], cfg["D"], cfg["K"]
     pk = packed.to(value.dtype)
-    # launch hints as the reference's findspec / findspec_bwd return them for G*D = 256
+    # launch hints as the reference's findspec / findspec_bwd return them
     from ops3d_b200.flash_deform_attn import findspec, findspec_bwd
     d_f, t_f = findspec(B, Q, G, D)
     d_b, t_b = findspec_bwd(B, Q, G, D)
@@ -295,13 +329,93 @@ def reference_cuda_block(cfg, value, shapes, lsi, packed, grad_out, steps=5, war
 
 
 # ---------------------------------------------------------------------------------------------
+# parity checks (outside the timed region)
+# ---------------------------------------------------------------------------------------------
+def _max_err(got, ref):
+    return (got.double().cpu() - ref.double().cpu()).abs().max().item()
+
+
+def parity_vs_oracle(cfg, capi, value, shapes, lsi, packed, grad_out, out, grad_packed, sample_q):
+    """N = 1: the CPU oracle on the first ``sample_q`` queries of batch element 0 against the full-size
+    volume.  ``out`` / ``grad_packed`` rows are taken from the full-size launch (rows are independent);
+    ``grad_value`` from a launch over exactly the sampled rows.  Returns (parity block, cpu_baseline block)."""
+    K, LK = cfg["K"], len(cfg["shapes"]) * cfg["K"]
+    v1, pk, go = value[:1], packed[:1, :sample_q].contiguous(), grad_out[:1, :sample_q].contiguous()
+    gv_gpu, gp_sub = capi.backward(v1, shapes, lsi, pk, go, K)
+    torch.cuda.synchronize()
+    same_rows = bool(torch.equal(gp_sub, grad_packed[:1, :sample_q]))  # the rows do not depend on which launch held them
+    tf, tfb, cores, (ref_out, ref_gv, ref_gp) = cpu_reference_pass(
+        v1.float().cpu(), shapes.cpu(), pk.float().cpu(), go.float().cpu(), K, steps=1, warmup=1)
+    tol = 1e-4 if cfg["vdt"] == "float32" else 2e-2
+    checks = {
+        "out": (_max_err(out[:1, :sample_q], ref_out), ref_out.abs().max().item()),
+        "grad_value": (_max_err(gv_gpu, ref_gv), ref_gv.abs().max().item()),
+        "grad_coords": (_max_err(grad_packed[:1, :sample_q, :, : 3 * LK], ref_gp[..., : 3 * LK]), ref_gp[..., : 3 * LK].abs().max().item()),
+        "grad_logits": (_max_err(grad_packed[:1, :sample_q, :, 3 * LK:], ref_gp[..., 3 * LK:]), ref_gp[..., 3 * LK:].abs().max().item()),
+    }
+    ok = all(e <= tol * max(1.0 if cfg["vdt"] == "float32" else 1e-30, m) for e, m in checks.values())
+    parity = {"ok": bool(ok), "against": "CPU oracle (PyTorch restatement of the reference's CPU implementation)",
+              "rows": f"first {sample_q} queries of batch element 0, full-size volume; grad_value from a launch over those rows",
+              "tolerance": f"{tol} x |ref|max" if cfg["vdt"] != "float32" else "1e-4 x max(1, |ref|max)",
+              "max_abs": {k: e for k, (e, _) in checks.items()}, "ref_max": {k: m for k, (_, m) in checks.items()},
+              "rows_identical_across_launches": same_rows}
+    return parity, cpu_block(cfg, sample_q, tf, tfb, cores)
+
+
+def parity_vs_unsharded(cfg, capi, dist, part, value, shapes, lsi, packed, grad_out, out, grad_value, grad_packed):
+    """N > 1: every rank gathers all ranks' rows, recomputes the whole step unsharded on its own GPU and
+    compares its out / grad_packed rows (exactly) and the reduced grad_value (2e-2 of the largest magnitude)."""
+    K = cfg["K"]
+    world = dist.get_world_size()
+    B, Q = cfg["B"], cfg["Q"]
+    nb, Qr = packed.shape[0], packed.shape[1]
+    sizes = torch.tensor([nb, Qr], device=value.device)
+    lo, hi = sizes.clone(), sizes.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    if not torch.equal(lo, hi):
+        return {"ok": None, "skipped": "ranks hold different row counts; gather not implemented for ragged shards"}
+
+    def gather_full(t):
+        parts = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(parts, t.contiguous())
+        if part.kind == "queries":       # [R, B, Qr, ...] -> [B, R*Qr, ...]
+            return parts.transpose(0, 1).reshape(B, world * Qr, *t.shape[2:]).contiguous()
+        return parts.reshape(B, Q, *t.shape[2:])  # batch / batch-groups: rank order is row order
+
+    pk_full, go_full = gather_full(packed), gather_full(grad_out)
+    out_ref = capi.forward(value, shapes, lsi, pk_full, K)
+    gv_ref, gp_ref = capi.backward(value, shapes, lsi, pk_full, go_full, K)
+    torch.cuda.synchronize()
+    rows = (slice(part.b_begin, part.b_end), slice(part.q_begin, part.q_end))
+    tol = 1e-4 if cfg["vdt"] == "float32" else 2e-2
+    errs, scales = {}, {}
+    for name, got, ref in (("out_rows", out, out_ref[rows]), ("grad_packed_rows", grad_packed, gp_ref[rows]),
+                           ("grad_value", grad_value, gv_ref)):
+        errs[name] = (got.float() - ref.float()).abs().max().item()
+        scales[name] = ref.float().abs().max().item()
+    ok = all(errs[k] <= tol * max(scales[k], 1e-30) for k in errs)
+    keys = sorted(errs)
+    stats = torch.tensor([0.0 if ok else 1.0] + [errs[k] for k in keys] + [scales[k] for k in keys],
+                         device=value.device, dtype=torch.float64)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    stats = stats.tolist()
+    errs = dict(zip(keys, stats[1:1 + len(keys)]))
+    scales = dict(zip(keys, stats[1 + len(keys):]))
+    return {"ok": stats[0] == 0.0, "against": "unsharded recomputation of the whole step on each rank's own GPU",
+            "max_abs": errs, "ref_max": scales, "rows_bit_equal": errs["out_rows"] == 0.0 and errs["grad_packed_rows"] == 0.0,
+            "tolerance": f"{tol} x |ref|max per tensor (rows are expected to be bit-equal, grad_value to differ by summation order)",
+            "ranks_checked": world}
+
+
+# ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
 def run_ours(args, cfg):
     import torch.distributed as dist
 
-    from ops3d_b200 import FlashDeformAttnFunction, capi
-    from ops3d_b200.sharded import PeerReducer, query_range, sharded_flash_deform_attn
+    from ops3d_b200 import capi
+    from ops3d_b200.host_stream import HostStreamedStep
+    from ops3d_b200.sharded import PeerReducer, partition
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -317,12 +431,13 @@ def run_ours(args, cfg):
     capi.load()
 
     B, Q, G, D, K = cfg["B"], cfg["Q"], cfg["G"], cfg["D"], cfg["K"]
-    qb, qe = query_range(Q, rank, world)
-    value, shapes, lsi, packed, grad_out = make_device_inputs(cfg, dev, qb, qe)
+    part = partition(B, Q, rank, world)
+    nb, Qr = part.b_end - part.b_begin, part.q_end - part.q_begin
+    value, shapes, lsi, packed, grad_out = make_device_inputs(cfg, dev, part)
+    value_local = value[part.b_begin:part.b_end]
     N = value.shape[1]
     vdt = value.dtype
-    out = torch.empty(B, qe - qb, G * D, dtype=vdt, device=dev)
-    grad_value = torch.empty_like(value)
+    out = torch.empty(nb, Qr, G * D, dtype=vdt, device=dev)
     grad_packed = torch.empty_like(packed)
     use_peer = world > 1 and args.reduce == "peer"
     reducer, peer_note = None, None
@@ -330,7 +445,7 @@ def run_ours(args, cfg):
         # symmetric-memory set-up can be unavailable on a machine (no peer access): all ranks agree, then
         # either all use the fused exchange or all fall back to NCCL all-reduce + cast
         try:
-            reducer = PeerReducer(value.shape, vdt, dev, spatial_shapes=shapes)
+            reducer = PeerReducer(value.shape, vdt, dev, spatial_shapes=shapes, part=part)
             ok = torch.ones(1, device=dev)
         except Exception as exc:  # noqa: BLE001
             peer_note = f"peer exchange unavailable ({type(exc).__name__}: {exc}); NCCL all-reduce used"
@@ -338,31 +453,34 @@ def run_ours(args, cfg):
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if ok.item() == 0:
             reducer, use_peer = None, False
-            os.environ["FDA_SHARDED_REDUCE"] = "nccl"  # the end-to-end leg follows suit
             peer_note = peer_note or "peer exchange unavailable on another rank; NCCL all-reduce used"
-    reducer_passes = reducer.passes if use_peer else None
     L = len(cfg["shapes"])
-    n_scratch = capi.scratch_bytes(value, packed, K)
-    scratch = torch.empty(n_scratch, dtype=torch.uint8, device=dev) if (n_scratch and not use_peer) else None
-    accum = None
+    grad_value = accum = scratch = None
     if not use_peer:
-        accum = torch.empty(value.shape, dtype=torch.float32, device=dev) if vdt != torch.float32 else grad_value
+        n_scratch = capi.scratch_bytes(value_local, packed, K)
+        scratch = torch.empty(n_scratch, dtype=torch.uint8, device=dev) if n_scratch else None
+        grad_value = torch.empty_like(value)
+        accum = torch.empty(value.shape, dtype=torch.float32, device=dev) if (vdt != torch.float32 or world > 1) else grad_value
 
     def step(ev=None):
+        nonlocal grad_value
         if ev: ev[0].record()
-        capi.forward(value, shapes, lsi, packed, K, out=out)
+        capi.forward(value_local, shapes, lsi, packed, K, out=out)
         if ev: ev[1].record()
         if use_peer:
-            # per batch element: scatter on this stream, fused NVLink reduce+cast overlapped on a side stream
-            reducer.backward(value, shapes, lsi, packed, grad_out, K, grad_packed=grad_packed)
+            # scatter on this stream, fused NVLink reduce+cast of finished pieces overlapped on a side stream
+            grad_value, _ = reducer.backward(value, shapes, lsi, packed, grad_out, K, grad_packed=grad_packed)
             if ev: ev[2].record(); ev[3].record()
             return
-        capi.backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, grad_packed, 0, L,
-                                        capi.BWD_ZERO_IMAGE | capi.BWD_FINALIZE, scratch=scratch)
+        if world > 1:
+            accum.zero_()   # the batch elements other ranks work on contribute zeros to the sum
+        capi.backward_accumulate_levels(value_local, shapes, lsi, packed, grad_out, K, accum[part.b_begin:part.b_end],
+                                        grad_packed, 0, L, (0 if world > 1 else capi.BWD_ZERO_IMAGE) | capi.BWD_FINALIZE,
+                                        scratch=scratch)
         if ev: ev[2].record()
         if world > 1:
             dist.all_reduce(accum)
-        if vdt != torch.float32:
+        if accum is not grad_value:
             capi.cast_grad_value(accum, grad_value)
         if ev: ev[3].record()
 
@@ -397,66 +515,79 @@ def run_ours(args, cfg):
     total_ms, fwd_ms, bwd_ms, tail_ms = times.tolist()
     ms_per_step = total_ms / args.steps
 
-    ref_cuda = None
-    if args.ref_cuda and world == 1:
-        ref_cuda = reference_cuda_block(cfg, value, shapes, lsi, packed, grad_out)
+    # ---- parity and baselines, outside the timed region ----------------------------------------------
+    parity, cpu_baseline, ref_cuda = None, None, None
+    if not args.no_parity:
+        if world > 1:
+            parity = parity_vs_unsharded(cfg, capi, dist, part, value, shapes, lsi, packed, grad_out, out, grad_value, grad_packed)
+        elif not args.no_cpu_baseline:
+            parity, cpu_baseline = parity_vs_oracle(cfg, capi, value, shapes, lsi, packed, grad_out, out, grad_packed,
+                                                    min(Q, CPU_SAMPLE_QUERIES))
+    if world == 1 and not args.no_ref_cuda:
+        try:
+            ref_cuda = reference_cuda_block(cfg, value, shapes, lsi, packed, grad_out)
+        except Exception as exc:  # noqa: BLE001  (a reported baseline must not take the bench down)
+            ref_cuda = {"unavailable": f"{type(exc).__name__}: {exc}"}
 
-    # ---- end to end through the public autograd API with host buffers --------------------------------
+    # ---- byte model and roofline (this rank's launches; all ranks do equal work) ----------------------
+    corners = count_in_range_corners(cfg, packed)
+    bm = byte_model(cfg, corners, nb, Qr, N)
+
+    # ---- end to end: host buffers in, host buffers out, through the package's host-buffer entry point -
     e2e_ms, h2d, d2h, e2e_steps = None, 0, 0, 0
     if not args.no_e2e:
-        e2e_steps = max(2, min(args.steps, 3))
-        host_in = [t.cpu().pin_memory() for t in (value, packed, grad_out)]
-        host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (out, grad_value, grad_packed)]
-        h2d = sum(t.numel() * t.element_size() for t in host_in)
-        d2h = sum(t.numel() * t.element_size() for t in host_out)
-        del out, grad_value, grad_packed, accum, reducer, scratch
+        e2e_steps = max(2, min(args.steps, 5))
+        host_value = value.cpu().pin_memory()
+        host_packed, host_go = packed.cpu().pin_memory(), grad_out.cpu().pin_memory()
+        host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        host_gv = torch.empty(value.shape, dtype=vdt).pin_memory()
+        host_gp = torch.empty(packed.shape, dtype=packed.dtype).pin_memory()
+        del out, grad_value, grad_packed, accum, scratch, value, value_local, packed, grad_out
         torch.cuda.empty_cache()
+        streamed = HostStreamedStep(host_value.shape, vdt, host_packed.shape, host_packed.dtype, K, shapes, lsi, dev,
+                                    reducer=reducer)
 
         def e2e_step():
-            v = host_in[0].to(dev, non_blocking=True).requires_grad_(True)
-            pk = host_in[1].to(dev, non_blocking=True).requires_grad_(True)
-            go = host_in[2].to(dev, non_blocking=True)
-            if world > 1:
-                o = sharded_flash_deform_attn(v, shapes, lsi, pk, 64, K)
-            else:
-                o = FlashDeformAttnFunction.apply(v, shapes, lsi, pk, 64, K, True)
-            o.backward(go)
-            host_out[0].copy_(o.detach(), non_blocking=True)
-            host_out[1].copy_(v.grad, non_blocking=True)
-            host_out[2].copy_(pk.grad, non_blocking=True)
+            streamed.run(host_value, host_packed, host_go, host_out, host_gv, host_gp)
 
-        e2e_step()
+        for _ in range(2):
+            e2e_step()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches_e2e0 = capi.KERNEL_LAUNCHES
         e0.record()
         for _ in range(e2e_steps):
             e2e_step()
         e1.record()
         torch.cuda.synchronize()
-        e2e_ms = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=dev, dtype=torch.float64)
+        e2e_launches = (capi.KERNEL_LAUNCHES - launches_e2e0) // e2e_steps
+        h2d, d2h = streamed.h2d_bytes, streamed.d2h_bytes
+        e2e_t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=dev, dtype=torch.float64)
         if world > 1:
-            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-        e2e_ms = e2e_ms.item()
-        if sampler:
-            sampler.stop()
+            dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+        e2e_ms = e2e_t.item()
+    if sampler:
+        sampler.stop()
 
-    # ---- byte model and roofline (this rank's launches; all ranks do equal work) ----------------------
-    corners = count_in_range_corners(cfg, packed)
-    bm = byte_model(cfg, corners, B, qe - qb, N)
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     else:
         peak, peak_src = 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
     achieved = bm["bwd_kernel"] / (bwd_ms * 1e-3) / 1e9
+    traffic, traffic_how = (measured_traffic(args.config) if (world == 1 and not args.batch and not args.queries)
+                            else (None, "captured for the full single-GPU launch only"))
     roofline = {
         "bound": "hbm",
         "kernel": "backward pass = zero-fill + slab binning + fda_backward_binned_kernel + fda_backward_kernel (one C-ABI call)",
         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-        "traffic": (NCU_BACKWARD_TRAFFIC_BYTES.get(args.config) if (world == 1 and not args.batch and not args.queries) else None),
-        "traffic_source": "ncu capture of a 1/16-row case scaled x16 (profiles/), both backward kernels",
+        "model": "gather model: every in-range corner row gathered (value dtype) and scattered (fp32) counts, plus the streamed "
+                 "rows; part of it is served by L2, so frac can exceed 1 -- dram_frac is the measured DRAM share",
+        "traffic": traffic, "traffic_source": traffic_how,
+        "dram_achieved": (traffic / (bwd_ms * 1e-3) / 1e9) if traffic else None,
+        "dram_frac": (traffic / (bwd_ms * 1e-3) / 1e9 / peak) if traffic else None,
         "peak_source": peak_src, "algorithmic_bytes_per_launch": bm["bwd_kernel"], "ms_per_launch": bwd_ms,
         "fwd_kernel": {"achieved": bm["fwd"] / (fwd_ms * 1e-3) / 1e9, "frac": bm["fwd"] / (fwd_ms * 1e-3) / 1e9 / peak,
                        "algorithmic_bytes_per_launch": bm["fwd"], "ms_per_launch": fwd_ms},
@@ -467,33 +598,44 @@ def run_ours(args, cfg):
     }
 
     if rank == 0:
+        sharding = "none"
+        if world > 1:
+            how = {"batch": f"{nb} whole batch element(s) per rank (no cross-rank sum; finished images cast and broadcast)",
+                   "batch-groups": f"{len(part.group)} ranks per batch element split its queries; partial fp32 images summed within the group",
+                   "queries": f"queries of every batch element split over all {world} ranks"}[part.kind]
+            sharding = (how + ", value replicated; exchange = " +
+                        ("fused peer-memory reduce+cast kernel pipelined with the scatter kernels" if use_peer
+                         else "NCCL all-reduce, then cast"))
         line = {
             "metric": METRIC, "value": B / (ms_per_step * 1e-3), "fwd_value": B / (fwd_ms * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "ms_fwd": fwd_ms, "ms_bwd_kernel": bwd_ms, "ms_reduce_and_cast": tail_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 value / f32 offsets, f32 accumulate" if cfg["vdt"] == "bfloat16" else "f32",
-            "data": "synthetic",
-            "config": {"workload": cfg["name"], "B": B, "Lq": Q, "N": N, "G": G, "D": D, "K": K, "levels": cfg["shapes"],
-                       "sharding": (f"queries/{world}, value replicated, grad_value fp32 images summed by "
-                                    + ("a fused peer-memory reduce+cast kernel overlapped per batch element" if use_peer
-                                       else "NCCL all-reduce, then cast")) if world > 1 else "none",
-                       "l2": "inputs larger than L2 (no flush needed)" if bm["fwd_bwd"] > 4e8 else "inputs smaller than L2",
-                       **({"note": peer_note} if peer_note else {})},
+            "data": "synthetic", "config": config_block(cfg), "sharding": sharding,
             "roofline": roofline,
-            "e2e": {"value": (B / (e2e_ms * 1e-3)) if e2e_ms else None, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "e2e": {"value": (B / (e2e_ms * 1e-3)) if e2e_ms else None, "unit": "samples/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "how": "HostStreamedStep: query chunks double-buffered over upload / compute / download streams"
+                           + ("; bytes are this rank's (each rank uploads its rows and its batch element(s) of value, "
+                              "downloads its rows and 1/N of grad_value)" if world > 1 else "")},
             "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
+        if peer_note:
+            line["note"] = peer_note
+        if parity is not None:
+            line["parity"] = parity
         if ref_cuda is not None:
             line["reference_cuda"] = ref_cuda
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline_block(cfg)
+        if cpu_baseline is not None:
+            line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and parity.get("ok") is False:
+        raise SystemExit("parity check failed: " + json.dumps(parity))
 
 
 def main():
@@ -503,13 +645,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle pass (and with it the N=1 parity block)")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity checks")
     ap.add_argument("--reduce", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the fp32 grad_value images are summed (fused peer-memory kernel, or NCCL all-reduce + cast)")
     ap.add_argument("--batch", type=int, default=0, help="override B (smaller case for profiler captures)")
     ap.add_argument("--queries", type=int, default=0, help="override Lq (smaller case for profiler captures)")
-    ap.add_argument("--ref-cuda", action="store_true",
-                    help="also time the reference's own CUDA kernels (needs baseline/_ref/ops3d_ref_C.so; N=1)")
+    ap.add_argument("--no-ref-cuda", action="store_true",
+                    help="do not time the reference's own CUDA kernels (timed by default at N=1 when baseline/_ref/ops3d_ref_C.so exists)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])

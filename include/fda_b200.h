@@ -91,18 +91,30 @@ int fda_forward(const void *value, const int64_t *spatial_shapes, const int64_t 
 /*
  * Bytes of device workspace fda_backward needs for this problem: the fp32 accumulation image of
  * grad_value for 16-bit values (batch*num_value*num_heads*head_dim*4, rounded up to 256; none for
- * an fp32 value, which accumulates in place) plus fda_backward_scratch_bytes().
+ * an fp32 value, which accumulates in place) plus, when the slab-binned path applies,
+ * fda_backward_scratch_bytes().
  */
-size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int num_query,
-                                    int num_points, int value_dtype);
+size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
+                                    int num_points, int value_dtype, int packed_dtype);
 
 /*
- * Bytes of scratch for the slab-binned handling of the largest pyramid level: slab counters plus
- * one 8-byte entry per (row, point) of one level.  0 when binning cannot pay off (the gradient
- * image of one batch element fits the device's L2 budget) or is switched off (FDA_BINNING=0).
+ * Bytes of scratch for the backward launches that hand work to one another:
+ *   - the slab-binned handling of the largest pyramid level: slab counters plus one 8-byte entry per
+ *     (row, point) of one level; 0 when binning cannot pay off (the gradient image of one batch
+ *     element fits the device's L2 budget) or is switched off (FDA_BINNING=0);
+ *   - for 16-bit offsets/logits, an fp32 plane [batch][num_query*num_heads][num_levels*num_points]
+ *     that carries the raw logit gradients from launch to launch unrounded (with fp32 offsets the
+ *     logit slots of grad_sampling_loc_attn serve, bit for bit).
  * Without scratch the backward still works, through the plain scatter kernel alone.
  */
-size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_query, int num_points);
+size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
+                                  int num_points, int packed_dtype);
+
+/*
+ * The library reads its tuning knobs (FDA_* environment variables) once, when it is loaded;
+ * fda_reload_config re-reads them.  Not thread-safe against concurrent launches.
+ */
+void fda_reload_config(void);
 
 /*
  * Backward: grad_value (scatter-add of softmax_i * w_corner * grad_output through fp32 vector
@@ -157,7 +169,9 @@ int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_element
  * (a single launch over all levels uses FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE).  Between launches
  * grad_sampling_loc_attn holds intermediate values; it is final after the FINALIZE launch.
  * scratch (fda_backward_scratch_bytes() bytes, 256-byte aligned, may be NULL) enables the
- * slab-binned path for the largest level when it is part of the range.
+ * slab-binned path for the largest level when it is part of the range, and keeps the logit
+ * gradients handed from launch to launch in fp32 when the offsets are 16-bit (without it they pass
+ * through grad_sampling_loc_attn and are rounded to 16 bits once more on the way).
  * No counterpart in the reference.
  */
 #define FDA_BWD_ZERO_IMAGE 1
@@ -211,6 +225,18 @@ int fda_peer_reduce_cast(const float *const *peer_images, void *const *peer_outp
                          size_t num_elements, int value_dtype, void *stream);
 
 /*
+ * The same exchange when only a GROUP of ranks holds partial sums of this range of the image (the
+ * batch-aligned partition: the ranks that share one batch element), while every rank of the job
+ * needs the result: group_images is a HOST array of `group_size` DEVICE pointers indexed by rank
+ * within the group (own image at `group_rank`); this rank sums slice `group_rank` of `group_size`
+ * equal slices and stores the converted result into all `world` peer_outputs.  A group of one is a
+ * cast + broadcast.  Same barrier contract as fda_peer_reduce_cast.  No counterpart in the reference.
+ */
+int fda_group_reduce_cast(const float *const *group_images, int group_size, int group_rank,
+                          void *const *peer_outputs, int world, int rank,
+                          size_t num_elements, int value_dtype, void *stream);
+
+/*
  * Push variant of the same exchange, in two calls with a cross-rank barrier between them (and the
  * usual one after): fda_peer_push_partials stores the slices of the local image that other ranks
  * own into their staging areas (peer_staging: HOST array of `world` DEVICE pointers, each area
@@ -258,7 +284,10 @@ int fda_pack_sampling(const void *offsets, const void *reference_points, const v
  * Returns FDA_ERR_TOO_LARGE_STATIC when a 16-bit grad_value has more than
  * FDA_NOALLOC_MAX_ELEMENTS elements (fp32 values accumulate in place and have no limit).
  * The first call on each device looks up the array's device address (that device must be
- * current); make that first call before any stream capture starts.  All calls share the one
+ * current); with lazy module loading that lookup is also what places the 64 MiB on the device,
+ * so make that first call (any small problem will do) at start-up: before a memory pool takes
+ * the rest of the GPU -- afterwards it can fail with FDA_ERR_CUDA / out of memory, see
+ * fda_last_cuda_error() -- and before any stream capture starts.  All calls share the one
  * array: calls that overlap on a GPU race with each other, so keep them ordered.  The array is
  * not cleared between calls; each call zeroes the part it uses before accumulating.
  */

@@ -55,7 +55,22 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     if not force and _newer(LIB, srcs):
         return LIB
     units = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
-    _run([_nvcc(), *NVCC_FLAGS, *units, "-o", LIB], verbose)
+    # one nvcc per translation unit, side by side, then one link
+    objdir = os.path.join(PKG, "_obj")
+    os.makedirs(objdir, exist_ok=True)
+    compile_flags = [f for f in NVCC_FLAGS if f != "-shared"]
+    extra = os.environ.get("FDA_NVCC_EXTRA", "").split()  # e.g. -DFDA_BWD_MIN_BLOCKS=3 for experiments
+    objs = [os.path.join(objdir, os.path.basename(u)[:-3] + ".o") for u in units]
+    procs = []
+    for u, o in zip(units, objs):
+        cmd = [_nvcc(), *compile_flags, *extra, "-c", u, "-o", o]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        procs.append((cmd, subprocess.Popen(cmd)))
+    for cmd, proc in procs:
+        if proc.wait() != 0:
+            raise subprocess.CalledProcessError(proc.returncode, cmd)
+    _run([_nvcc(), *NVCC_FLAGS, *objs, "-o", LIB], verbose)
     return LIB
 
 

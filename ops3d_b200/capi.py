@@ -19,7 +19,7 @@ EXPORTS = (
     "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
     "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
-    "fda_pack_sampling",
+    "fda_pack_sampling", "fda_reload_config", "fda_group_reduce_cast",
 )
 BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE = 1, 2, 4, 8
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
@@ -57,8 +57,11 @@ def load() -> ctypes.CDLL:
     lib.fda_version.restype = i
     lib.fda_forward.argtypes = [vp] * 5 + [i] * 13 + [vp]
     lib.fda_forward.restype = i
-    lib.fda_backward_workspace_bytes.argtypes = [i] * 7
-    lib.fda_backward_scratch_bytes.argtypes = [i] * 6
+    lib.fda_backward_workspace_bytes.argtypes = [i] * 9
+    lib.fda_backward_scratch_bytes.argtypes = [i] * 8
+    lib.fda_reload_config.restype = None
+    lib.fda_group_reduce_cast.argtypes = [vp, i, i, vp, i, i, sz, i, vp]
+    lib.fda_group_reduce_cast.restype = i
     lib.fda_backward_scratch_bytes.restype = sz
     lib.fda_backward_workspace_bytes.restype = sz
     lib.fda_backward.argtypes = [vp] * 8 + [sz] + [i] * 12 + [vp]
@@ -120,14 +123,32 @@ def forward(value, shapes, lsi, packed, K, im2col_step=64, use_reg=True, out=Non
     return out
 
 
+def reload_config():
+    """Makes the library re-read its FDA_* environment knobs (it reads them once, when loaded)."""
+    load().fda_reload_config()
+
+
+def _levels(packed, K) -> int:
+    return packed.shape[-1] // (4 * K)
+
+
 def workspace_bytes(value, packed, K) -> int:
     B, N, G, D = value.shape
-    return int(load().fda_backward_workspace_bytes(B, N, G, D, packed.shape[1], K, DTYPE_CODE[value.dtype]))
+    return int(load().fda_backward_workspace_bytes(B, N, G, D, _levels(packed, K), packed.shape[1], K,
+                                                   DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype]))
 
 
 def scratch_bytes(value, packed, K) -> int:
+    """Bytes of scratch for launches that hand work to one another (slab lists; fp32 logit-gradient plane for
+    16-bit offsets)."""
     B, N, G, D = value.shape
-    return int(load().fda_backward_scratch_bytes(B, N, G, D, packed.shape[1], K))
+    return int(load().fda_backward_scratch_bytes(B, N, G, D, _levels(packed, K), packed.shape[1], K, DTYPE_CODE[packed.dtype]))
+
+
+def binning_applies(value, packed, K) -> bool:
+    """True when the slab-binned path handles the largest level of this problem (given scratch)."""
+    B, N, G, D = value.shape
+    return int(load().fda_backward_scratch_bytes(B, N, G, D, _levels(packed, K), packed.shape[1], K, 0)) > 0
 
 
 def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value=None, grad_packed=None,
@@ -150,7 +171,7 @@ def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype],
             im2col_step, 1, 0, _stream(value)))
     # scatter kernel (+ count, scan, fill, binned kernels when the workspace includes binning scratch) + cast
-    _count(1 + (4 if scratch_bytes(value, packed, K) else 0) + (1 if value.dtype != torch.float32 else 0))
+    _count(1 + (4 if binning_applies(value, packed, K) else 0) + (1 if value.dtype != torch.float32 else 0))
     return grad_value, grad_packed
 
 
@@ -181,7 +202,7 @@ def backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, g
             level_begin, level_end, flags,
             scratch.data_ptr() if scratch is not None else None,
             scratch.numel() * scratch.element_size() if scratch is not None else 0, _stream(value)))
-    binned_here = scratch is not None and scratch_bytes(value, packed, K) and not (flags & BWD_BINNED_DONE)
+    binned_here = scratch is not None and binning_applies(value, packed, K) and not (flags & BWD_BINNED_DONE)
     _count(1 + (4 if binned_here else 0))
     return grad_packed
 
@@ -244,6 +265,18 @@ def peer_reduce_cast(image_ptrs, output_ptrs, rank, num_elements, dtype, device,
     with torch.cuda.device(device):
         check(load().fda_peer_reduce_cast(imgs, outs, world, rank, num_elements, DTYPE_CODE[dtype],
                                           torch.cuda.current_stream(device).cuda_stream))
+    _count(1)
+
+
+def group_reduce_cast(group_image_ptrs, group_rank, output_ptrs, rank, num_elements, dtype, device, byte_offsets=(0, 0)):
+    """``fda_group_reduce_cast``: like ``peer_reduce_cast`` but only the ranks of one group hold partial images
+    (``group_image_ptrs``, indexed by rank within the group); the result goes to every rank's output."""
+    gsize, world = len(group_image_ptrs), len(output_ptrs)
+    imgs = (ctypes.c_void_p * gsize)(*[p + byte_offsets[0] for p in group_image_ptrs])
+    outs = (ctypes.c_void_p * world)(*[p + byte_offsets[1] for p in output_ptrs])
+    with torch.cuda.device(device):
+        check(load().fda_group_reduce_cast(imgs, gsize, group_rank, outs, world, rank, num_elements, DTYPE_CODE[dtype],
+                                           torch.cuda.current_stream(device).cuda_stream))
     _count(1)
 
 

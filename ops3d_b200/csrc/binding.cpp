@@ -109,7 +109,7 @@ std::vector<at::Tensor> flash_deform_attn_backward(const at::Tensor &value, cons
     if (d.Q == 0 || d.B == 0) return {at::zeros_like(value), at::zeros_like(sampling_loc_attn)};
     at::Tensor grad_value = at::empty_like(value);
     at::Tensor grad_packed = at::empty_like(sampling_loc_attn);
-    const size_t ws_bytes = fda_backward_workspace_bytes(d.B, d.N, d.G, d.D, d.Q, K, vdt);
+    const size_t ws_bytes = fda_backward_workspace_bytes(d.B, d.N, d.G, d.D, d.L, d.Q, K, vdt, pdt);
     at::Tensor workspace;
     void *ws_ptr = nullptr;
     if (ws_bytes > 0) {

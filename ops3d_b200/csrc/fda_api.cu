@@ -2,6 +2,7 @@
 // dispatch and kernel launches.  No torch types, no allocation, nothing but the CUDA runtime.
 #include "../../include/fda_b200.h"
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -11,6 +12,7 @@
 
 #include "fda_backward.cuh"
 #include "fda_backward_binned.cuh"
+#include "fda_config.h"
 #include "fda_forward.cuh"
 
 namespace {
@@ -47,29 +49,49 @@ int validate(const Shape &s, int im2col_step) {
     return FDA_OK;
 }
 
-// Bytes of re-used data the kernels may mark "evict last": a fraction of the device's L2
-// (FDA_L2_KEEP_FRACTION overrides the default; 0 disables the hints' effect).
+fda::Config read_config() {
+    fda::Config c;
+    c.l2_keep_fraction = 0.7;
+    c.binning = 1;
+    c.bin_slab_mb = 16.0;  // 8-16 MB of image per slab measured best on B200 (value rows of the slab add half of that)
+    c.bin_grid_x = 592;    // 4 blocks per SM's worth of 2 resident blocks: each block strides over its slab's list
+    c.pair_rows = 1;
+    c.forced_variant = 0;
+    c.peer_reduce_blocks = 32;
+    if (const char *e = std::getenv("FDA_L2_KEEP_FRACTION")) c.l2_keep_fraction = std::atof(e);
+    if (c.l2_keep_fraction < 0) c.l2_keep_fraction = 0;
+    if (const char *e = std::getenv("FDA_BINNING")) c.binning = std::atoi(e) != 0;
+    if (const char *e = std::getenv("FDA_BIN_SLAB_MB")) c.bin_slab_mb = std::atof(e);
+    if (const char *e = std::getenv("FDA_BIN_GRID_X")) c.bin_grid_x = std::atoi(e);
+    if (c.bin_grid_x < 1) c.bin_grid_x = 1;
+    if (const char *e = std::getenv("FDA_PAIR_ROWS")) c.pair_rows = std::atoi(e) != 0;
+    if (const char *e = std::getenv("FDA_FORCE_VARIANT")) {
+        if (!std::strcmp(e, "reg")) c.forced_variant = 1;
+        if (!std::strcmp(e, "smem")) c.forced_variant = 2;
+    }
+    if (const char *e = std::getenv("FDA_PEER_REDUCE_BLOCKS")) c.peer_reduce_blocks = std::atoi(e);
+    if (c.peer_reduce_blocks < 1) c.peer_reduce_blocks = 1;
+    return c;
+}
+
+fda::Config g_config = read_config();
+
+// L2 size of the current device, looked up once per device.
+constexpr int kMaxDevices = 64;
+std::atomic<int> g_l2_bytes[kMaxDevices];
+
+// Bytes of re-used data the kernels may mark "evict last": a fraction of the device's L2.
 unsigned long long l2_keep_budget() {
-    static std::mutex mu;
-    static std::map<int, int> l2_bytes;
-    double frac = 0.7;
-    if (const char *e = std::getenv("FDA_L2_KEEP_FRACTION")) frac = std::atof(e);
-    if (frac < 0) frac = 0;
+    const double frac = g_config.l2_keep_fraction;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) {  // no device (sizing queries on a build machine): B200's 126 MB
-        (void)cudaGetLastError();
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        (void)cudaGetLastError();  // no device (sizing queries on a build machine): B200's 126 MB
         return (unsigned long long)(frac * 126.0 * 1024 * 1024);
     }
-    int l2 = 0;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        auto it = l2_bytes.find(dev);
-        if (it == l2_bytes.end()) {
-            if (cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev) != cudaSuccess) l2 = 0;
-            l2_bytes[dev] = l2;
-        } else {
-            l2 = it->second;
-        }
+    int l2 = g_l2_bytes[dev].load(std::memory_order_relaxed);
+    if (l2 == 0) {
+        if (cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev) != cudaSuccess || l2 <= 0) l2 = 1;
+        g_l2_bytes[dev].store(l2, std::memory_order_relaxed);
     }
     return (unsigned long long)(frac * (double)l2);
 }
@@ -133,15 +155,6 @@ inline dim3 row_grid(const fda::Problem &p, int threads) {
     return dim3((unsigned)((p.rows_per_b + rows_per_block - 1) / rows_per_block), (unsigned)p.B, 1);
 }
 
-// 0: let the library choose, 1: register-staged, 2: shared-memory-staged
-int forced_forward_variant() {
-    const char *e = std::getenv("FDA_FORCE_VARIANT");
-    if (!e) return 0;
-    if (!std::strcmp(e, "reg")) return 1;
-    if (!std::strcmp(e, "smem")) return 2;
-    return 0;
-}
-
 template <typename VT, typename PT>
 int launch_forward(fda::Problem p, bool stage, cudaStream_t st) {
     if (stage) {
@@ -160,30 +173,40 @@ int launch_forward(fda::Problem p, bool stage, cudaStream_t st) {
 
 inline size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
 
-// Scratch of the slab-binned path: counters [3][B][kMaxSlabs] then entries [B][rows_per_b*K] (8 bytes each).
-// Zero when binning cannot apply to this problem (image of one batch element fits the L2 budget, or
-// the entry index would not fit 32 bits, or FDA_BINNING=0).
+// Scratch layout: [slab counters [3][B][kMaxSlabs]] [entries [B][rows_per_b*K], 8 bytes each] [dalpha plane].
+// The binning part is zero-sized when binning cannot apply to this problem (image of one batch element fits
+// the L2 budget, or the entry index would not fit 32 bits, or FDA_BINNING=0).
 size_t bin_scratch_bytes(int B, int N, int G, int D, int Q, int K) {
-    if (const char *e = std::getenv("FDA_BINNING")) if (std::atoi(e) == 0) return 0;
+    if (!g_config.binning) return 0;
     if (B <= 0 || N <= 0 || G <= 0 || D <= 0 || Q <= 0 || K <= 0 || K > 8) return 0;
     if ((unsigned long long)N * G * D * 4ull <= l2_keep_budget()) return 0;
     const unsigned long long cap = (unsigned long long)Q * G * K;
     if (cap >= (1ull << 32)) return 0;
-    return round256((size_t)3 * B * fda::kMaxSlabs * sizeof(unsigned int)) + (size_t)B * cap * sizeof(uint2);
+    return round256(round256((size_t)3 * B * fda::kMaxSlabs * sizeof(unsigned int)) + (size_t)B * cap * sizeof(uint2));
 }
 
-// Target size of one slab's share of the fp32 image (FDA_BIN_SLAB_MB overrides).
+// fp32 plane [B][Q*G][L*K] that carries raw dalpha between launches; only 16-bit offsets need it (with fp32
+// offsets the logit slots of grad_sampling_loc_attn hold the same bits).
+size_t dalpha_plane_bytes(int B, int G, int L, int Q, int K, int pdt) {
+    if (pdt == FDA_DTYPE_F32 || B <= 0 || G <= 0 || L <= 0 || Q <= 0 || K <= 0) return 0;
+    return round256((size_t)B * Q * G * L * K * sizeof(float));
+}
+
+// Target size of one slab's share of the fp32 image.
 unsigned long long bin_slab_bytes_setting() {
-    double slab_mb = 16.0;  // share of the fp32 image per slab (value rows of the slab add half of that); 8-16 MB measured best on B200
-    if (const char *e = std::getenv("FDA_BIN_SLAB_MB")) slab_mb = std::atof(e);
-    unsigned long long b = (unsigned long long)(slab_mb * 1048576.0);
+    unsigned long long b = (unsigned long long)(g_config.bin_slab_mb * 1048576.0);
     return b < 4096 ? 4096 : b;
 }
 
-// Point the problem at the caller's binning scratch when it is present and large enough.
-void attach_bin_scratch(fda::Problem &p, const Shape &s, void *scratch, size_t scratch_bytes) {
-    const size_t need = bin_scratch_bytes(s.B, s.N, s.G, s.D, s.Q, s.K);
-    if (need == 0 || !scratch || scratch_bytes < need || !aligned16(scratch)) return;
+// Point the problem at the caller's scratch when it is present and large enough: the slab lists, and for
+// 16-bit offsets the dalpha plane behind them (binning is not used without its plane in that case).
+void attach_scratch(fda::Problem &p, const Shape &s, void *scratch, size_t scratch_bytes) {
+    if (!scratch || !aligned16(scratch)) return;
+    const size_t bin_need = bin_scratch_bytes(s.B, s.N, s.G, s.D, s.Q, s.K);
+    const size_t plane_need = dalpha_plane_bytes(s.B, s.G, s.L, s.Q, s.K, s.pdt);
+    if (scratch_bytes < bin_need + plane_need) return;
+    if (plane_need) p.dalpha = reinterpret_cast<float *>(static_cast<char *>(scratch) + bin_need);
+    if (bin_need == 0) return;
     p.bin_allowed = 1;
     p.bin_counters = static_cast<unsigned int *>(scratch);
     p.bin_entries = reinterpret_cast<uint2 *>(static_cast<char *>(scratch) +
@@ -196,7 +219,7 @@ void attach_bin_scratch(fda::Problem &p, const Shape &s, void *scratch, size_t s
 // rows scatter as a team so that every reduction request covers a whole 128-byte line of the image.
 template <typename VT>
 bool pair_rows(const fda::Problem &p) {
-    if (const char *e = std::getenv("FDA_PAIR_ROWS")) if (std::atoi(e) == 0) return false;
+    if (!g_config.pair_rows) return false;
     return fda::Vec16<VT>::kCPL == 8 && p.gs_log2 == 2 && p.lpg == 4;
 }
 
@@ -224,9 +247,7 @@ int launch_bin_prepare(const fda::Problem &p, cudaStream_t st) {
 template <typename VT, typename PT>
 int launch_binned_slabs(const fda::Problem &p, cudaStream_t st) {
     // x: blocks striding over one slab's list; y: slab (slabs run one after the other); z: batch element
-    int gx = 592;  // 4 blocks per SM's worth of 2 resident blocks: each block strides over its slab's list
-    if (const char *e = std::getenv("FDA_BIN_GRID_X")) gx = std::atoi(e);
-    if (gx < 1) gx = 1;
+    const int gx = g_config.bin_grid_x;
     const dim3 grid((unsigned)gx, fda::kMaxSlabs, (unsigned)p.B);
     if (pair_rows<VT>(p)) fda::fda_backward_binned_kernel<VT, PT, true><<<grid, fda::kThreads, 0, st>>>(p);
     else fda::fda_backward_binned_kernel<VT, PT, false><<<grid, fda::kThreads, 0, st>>>(p);
@@ -272,7 +293,14 @@ int launch_backward(fda::Problem p, cudaStream_t st) {
 
 }  // namespace
 
+namespace fda {
+const Config &config() { return g_config; }
+void record_cuda_error(int e) { g_last_cuda_error = e; }
+}  // namespace fda
+
 extern "C" {
+
+void fda_reload_config(void) { g_config = read_config(); }
 
 const char *fda_status_string(int status) {
     switch (status) {
@@ -311,21 +339,25 @@ int fda_forward(const void *value, const int64_t *spatial_shapes, const int64_t 
     // Staging choice per shape: with several rows per warp the packed rows of a warp are one
     // contiguous span, which the staged kernel reads with full-width coalesced loads.
     bool stage = !use_reg || p.gs_log2 <= 3;
-    const int forced = forced_forward_variant();
+    const int forced = g_config.forced_variant;
     if (forced == 1 && use_reg) stage = false;
     if (forced == 2) stage = true;
     return FDA_DISPATCH(value_dtype, packed_dtype, (launch_forward<VT, PT>(p, stage, static_cast<cudaStream_t>(stream))));
 }
 
-size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int num_query,
-                                    int num_points, int value_dtype) {
-    if (batch <= 0 || num_value <= 0 || num_heads <= 0 || head_dim <= 0) return 0;
-    const size_t image = value_dtype == FDA_DTYPE_F32 ? 0 : round256((size_t)batch * num_value * num_heads * head_dim * sizeof(float));
-    return image + bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points);
+size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
+                                  int num_points, int packed_dtype) {
+    return bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points) +
+           dalpha_plane_bytes(batch, num_heads, num_levels, num_query, num_points, packed_dtype);
 }
 
-size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_query, int num_points) {
-    return bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points);
+size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
+                                    int num_points, int value_dtype, int packed_dtype) {
+    if (batch <= 0 || num_value <= 0 || num_heads <= 0 || head_dim <= 0) return 0;
+    const size_t image = value_dtype == FDA_DTYPE_F32 ? 0 : round256((size_t)batch * num_value * num_heads * head_dim * sizeof(float));
+    // fda_backward hands dalpha from launch to launch only when the largest level is slab-binned
+    const size_t bin = bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points);
+    return image + (bin ? bin + dalpha_plane_bytes(batch, num_heads, num_levels, num_query, num_points, packed_dtype) : 0);
 }
 
 int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
@@ -356,7 +388,7 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
     p.resume = (flags & FDA_BWD_RESUME) ? 1 : 0;
     p.finalize = (flags & FDA_BWD_FINALIZE) ? 1 : 0;
     // slab-binned handling of the largest level, when the caller gave scratch for it
-    attach_bin_scratch(p, s, scratch, scratch_bytes);
+    attach_scratch(p, s, scratch, scratch_bytes);
     p.binned_elsewhere = (flags & FDA_BWD_BINNED_DONE) ? 1 : 0;
     if (p.binned_elsewhere && !p.bin_allowed) return FDA_ERR_WORKSPACE;
     return FDA_DISPATCH(value_dtype, packed_dtype, (launch_backward<VT, PT>(p, st)));
@@ -393,7 +425,7 @@ int fda_backward_binned_part(const void *value, const int64_t *spatial_shapes, c
     fda::Problem p = make_problem(s);
     p.value = value; p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn;
     p.grad_out = grad_output; p.accum = accum; p.grad_packed = grad_sampling_loc_attn;
-    attach_bin_scratch(p, s, scratch, scratch_bytes);
+    attach_scratch(p, s, scratch, scratch_bytes);
     if (!p.bin_allowed) return FDA_ERR_WORKSPACE;
     p.slab_part = part;
     p.slab_parts = parts;
@@ -451,7 +483,8 @@ int fda_backward(const void *value, const int64_t *spatial_shapes, const int64_t
                  int im2col_step, int d_stride, int block_thread, void *stream) {
     (void)d_stride; (void)block_thread;
     if (!grad_value) return FDA_ERR_NULL_POINTER;
-    const size_t need = fda_backward_workspace_bytes(batch, num_value, num_heads, head_dim, num_query, num_points, value_dtype);
+    const size_t need = fda_backward_workspace_bytes(batch, num_value, num_heads, head_dim, num_levels, num_query, num_points,
+                                                     value_dtype, packed_dtype);
     const size_t n = (size_t)batch * num_value * num_heads * head_dim;
     const size_t image_bytes = value_dtype == FDA_DTYPE_F32 ? 0 : round256(n * sizeof(float));
     float *accum = static_cast<float *>(grad_value);

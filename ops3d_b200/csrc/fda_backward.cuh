@@ -17,9 +17,10 @@
 //     instead of the reference's O((L*K)^2) Jacobian loop (:413-427).
 //
 // A launch may cover only some pyramid levels (level_mask).  A non-final launch leaves the raw
-// dalpha of its points in the logit slots of grad_packed; the final launch (`resume`) picks up
-// the finished slots of the other levels from grad_packed, adds its own and applies the soft-max
-// backward over all points.  This lets a multi-GPU caller finish the largest level first and
+// dalpha of its points in an fp32 plane of the caller's scratch (or, without one, in the logit
+// slots of grad_packed, which is exact for fp32 offsets only); the final launch (`resume`) picks up
+// the finished coordinate slots of the other levels from grad_packed and their dalpha from the
+// plane, adds its own and applies the soft-max backward over all points.  This lets a multi-GPU caller finish the largest level first and
 // exchange its part of the gradient image while the remaining levels are still being computed,
 // and lets the largest level be handled slab by slab (fda_backward_binned.cuh).
 #pragma once
@@ -213,13 +214,18 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
     if (s_resume) {
         // slots of levels handled by an earlier launch: finished coordinate gradients and raw dalpha
         const PT *prev = static_cast<const PT *>(p.grad_packed) + warp_elem0;
+        const float *prev_da = p.dalpha ? p.dalpha + ((size_t)b * p.rows_per_b + first) * (size_t)LK : nullptr;
         const int nvec = nrows * LK;
         for (int v = lane; v < nvec; v += 32) {
             const int r = v / LK;
             const int c = (v - r * LK) * 4;
             const int j = c < 3 * LK ? c / 12 : (c - 3 * LK) >> 2;
-            if (!((level_mask >> (j >> p.k_shift)) & 1))
-                *reinterpret_cast<float4 *>(wtile + r * p.row_stride + c) = load4_stream<PT>(prev + (size_t)v * 4);
+            if (!((level_mask >> (j >> p.k_shift)) & 1)) {
+                float4 f;
+                if (c >= 3 * LK && prev_da) f = __ldcs(reinterpret_cast<const float4 *>(prev_da + (size_t)r * LK + (c - 3 * LK)));
+                else f = load4_stream<PT>(prev + (size_t)v * 4);
+                *reinterpret_cast<float4 *>(wtile + r * p.row_stride + c) = f;
+            }
         }
         __syncwarp();
     }
@@ -289,10 +295,14 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
     // coalesced write-back of the finished gradient rows of this warp
     PT *dst = static_cast<PT *>(p.grad_packed) + warp_elem0;
     const int nvec = nrows * LK;
+    float *next_da = (!p.finalize && p.dalpha) ? p.dalpha + ((size_t)b * p.rows_per_b + first) * (size_t)LK : nullptr;
     for (int v = lane; v < nvec; v += 32) {
         const int r = v / LK;
         const int c = (v - r * LK) * 4;
-        store4_stream<PT>(dst + (size_t)v * 4, *reinterpret_cast<const float4 *>(wtile + r * p.row_stride + c));
+        const float4 f = *reinterpret_cast<const float4 *>(wtile + r * p.row_stride + c);
+        store4_stream<PT>(dst + (size_t)v * 4, f);
+        // raw dalpha for the launch that finishes these rows, unrounded
+        if (next_da && c >= 3 * LK) __stcs(reinterpret_cast<float4 *>(next_da + (size_t)r * LK + (c - 3 * LK)), f);
     }
 }
 

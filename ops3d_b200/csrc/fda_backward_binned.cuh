@@ -17,7 +17,8 @@
 //                          level get their zero gradients written here
 //   fda_backward_binned_kernel  grid (x, slab, batch): one lane group per list entry -- dense work,
 //                          no divergence; same point_backward as the plain kernel; writes the point's
-//                          coordinate gradients and raw dalpha straight into grad_packed
+//                          coordinate gradients straight into grad_packed and its raw dalpha into the
+//                          fp32 dalpha plane (into grad_packed's logit slot when there is no plane)
 //
 // The remaining levels, and the soft-max backward over all points, are done afterwards by
 // fda_backward_kernel with `resume`.  Nothing here waits on another block.
@@ -173,7 +174,8 @@ __global__ void __launch_bounds__(kThreads) fda_bin_fill_kernel(const Problem p)
                     pos[j] = atomicAdd(&hist[slab[j]], 1u);
                 } else {  // no corner inside the level: the point contributes nothing, its gradients are zero
                     store1<PT>(gr + 3 * i, 0.f); store1<PT>(gr + 3 * i + 1, 0.f); store1<PT>(gr + 3 * i + 2, 0.f);
-                    store1<PT>(gr + 3 * LK + i, 0.f);
+                    if (p.dalpha) p.dalpha[((size_t)b * p.rows_per_b + row) * (size_t)LK + i] = 0.f;
+                    else store1<PT>(gr + 3 * LK + i, 0.f);
                 }
             }
         }
@@ -287,7 +289,8 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
             PT *gr = static_cast<PT *>(p.grad_packed) + grow * (size_t)(4 * LK);
             const int i = lvl_first + k;
             store1<PT>(gr + 3 * i, gx); store1<PT>(gr + 3 * i + 1, gy); store1<PT>(gr + 3 * i + 2, gz);
-            store1<PT>(gr + 3 * LK + i, da);
+            if (p.dalpha) p.dalpha[grow * (size_t)LK + i] = da;  // unrounded, for the soft-max backward of the final launch
+            else store1<PT>(gr + 3 * LK + i, da);
         }
         ent_cur = ent_nxt; ent_nxt = ent_nn;
         x = xn; y = yn; z = zn;

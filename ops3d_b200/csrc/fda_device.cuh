@@ -65,6 +65,9 @@ struct Problem {
     unsigned long long bin_cap;          // entries per batch element = rows_per_b * K
     int slab_part, slab_parts;           // the binned kernel of this launch covers slabs [S*part/parts, S*(part+1)/parts)
     int binned_elsewhere;                // the binned launches for this call were issued separately (plain kernel only)
+    // fp32 plane [B][rows_per_b][LK] that carries raw dalpha from launch to launch (binned -> plain, level range ->
+    // level range); null: the logit slots of grad_packed carry it (exact only when the packed dtype is fp32)
+    float *dalpha;
 };
 
 constexpr int kMaxSlabs = 64;

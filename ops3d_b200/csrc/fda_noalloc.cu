@@ -12,7 +12,14 @@
 // than that are rejected.  All calls share the one array, so two calls that overlap in time on
 // the same GPU (different streams, different threads) corrupt each other; issue them in order.
 // The array keeps whatever the last call left in it; each call clears the part it uses first.
+//
+// First call on a device: it resolves the array's device address.  With the CUDA runtime's lazy
+// module loading that lookup is also what loads this module onto the device and gives the array
+// its 64 MiB, so a process whose pool is about to claim the whole GPU should make one (tiny) call
+// at start-up, before the pool grows and before any stream capture; later calls only launch.
 #include "../../include/fda_b200.h"
+
+#include "fda_config.h"
 
 #include <cuda_runtime.h>
 
@@ -34,13 +41,16 @@ float *g_image_ptr[kMaxDevices] = {};
 int image_pointer(float **out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return FDA_ERR_CUDA;
+    if (e != cudaSuccess) { fda::record_cuda_error((int)e); return FDA_ERR_CUDA; }
     if (dev < 0 || dev >= kMaxDevices) return FDA_ERR_TOO_LARGE_STATIC;
     std::lock_guard<std::mutex> lock(g_mu);
     if (!g_image_ptr[dev]) {
         float *ptr = nullptr;
         e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_accum_image);
-        if (e != cudaSuccess || !ptr) return FDA_ERR_CUDA;
+        if (e != cudaSuccess || !ptr) {  // e.g. out of memory when the module cannot be loaded any more
+            fda::record_cuda_error((int)(e != cudaSuccess ? e : cudaErrorInvalidSymbol));
+            return FDA_ERR_CUDA;
+        }
         g_image_ptr[dev] = ptr;
     }
     *out = g_image_ptr[dev];

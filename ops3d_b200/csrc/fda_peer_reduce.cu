@@ -15,7 +15,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
+#include "fda_config.h"
 
 namespace {
 
@@ -61,8 +61,10 @@ template <> struct Out8<__half> {
 // issues all of its peer loads (2 x 16 bytes per unit and rank) before the first use, so that few
 // resident threads keep enough bytes in flight to cover NVLink latency while most SMs stay free
 // for the scatter kernel running beside it.
+// `world` images are summed (the ranks that hold partial sums of this range); the result goes to `n_out`
+// outputs (every rank of the job).
 template <typename VT, int WORLD, int UNROLL>
-__global__ void __launch_bounds__(512) fda_peer_reduce_cast_kernel(const PeerPtrs pp, const int world_rt,
+__global__ void __launch_bounds__(512) fda_peer_reduce_cast_kernel(const PeerPtrs pp, const int world_rt, const int n_out,
                                                                    size_t unit_begin, size_t unit_end) {
     constexpr int W = WORLD > 0 ? WORLD : kMaxPeers;
     const int world = WORLD > 0 ? WORLD : world_rt;
@@ -95,9 +97,7 @@ __global__ void __launch_bounds__(512) fda_peer_reduce_cast_kernel(const PeerPtr
                         a[4] += hi[j][p].x; a[5] += hi[j][p].y; a[6] += hi[j][p].z; a[7] += hi[j][p].w;
                     }
                 }
-#pragma unroll
-                for (int p = 0; p < W; ++p)
-                    if (p < world) Out8<VT>::store(pp.out[p], u, a);
+                for (int p = 0; p < n_out; ++p) Out8<VT>::store(pp.out[p], u, a);
             }
         }
     }
@@ -232,29 +232,30 @@ __global__ void __launch_bounds__(512) fda_peer_reduce_staged_kernel(const float
     }
 }
 
-int env_int(const char *name, int dflt) {
-    const char *e = std::getenv(name);
-    return e ? std::atoi(e) : dflt;
+inline int status_of(cudaError_t e) {
+    if (e == cudaSuccess) return FDA_OK;
+    fda::record_cuda_error((int)e);
+    return FDA_ERR_CUDA;
 }
 
 template <typename VT>
-cudaError_t launch(const PeerPtrs &pp, int world, size_t ub, size_t ue, cudaStream_t st) {
+cudaError_t launch(const PeerPtrs &pp, int n_in, int n_out, size_t ub, size_t ue, cudaStream_t st) {
     const size_t units = ue - ub;
     if (units == 0) return cudaSuccess;
     // Few, fat blocks: the kernel is bound by NVLink, not by SM throughput.  Measured with the exchange overlapped
     // with the scatter kernels: on 2 GPUs 16 to 1184 blocks take the same time; on 8 GPUs 8 / 16 / 32 blocks give
     // 13.7 / 9.1 / 8.6 ms per step (FDA_PEER_REDUCE_BLOCKS overrides).
-    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 32);
-    if (max_blocks < 1) max_blocks = 1;
+    const int max_blocks = fda::config().peer_reduce_blocks;
     const int threads = 512;
     size_t blocks = (units + threads - 1) / threads;
     if (blocks > (size_t)max_blocks) blocks = (size_t)max_blocks;
     const unsigned g = (unsigned)blocks;
-    switch (world) {
-        case 2: fda_peer_reduce_cast_kernel<VT, 2, 4><<<g, threads, 0, st>>>(pp, world, ub, ue); break;
-        case 4: fda_peer_reduce_cast_kernel<VT, 4, 2><<<g, threads, 0, st>>>(pp, world, ub, ue); break;
-        case 8: fda_peer_reduce_cast_kernel<VT, 8, 1><<<g, threads, 0, st>>>(pp, world, ub, ue); break;
-        default: fda_peer_reduce_cast_kernel<VT, 0, 1><<<g, threads, 0, st>>>(pp, world, ub, ue); break;
+    switch (n_in) {  // images x units in flight per thread = 8
+        case 1: fda_peer_reduce_cast_kernel<VT, 1, 8><<<g, threads, 0, st>>>(pp, n_in, n_out, ub, ue); break;
+        case 2: fda_peer_reduce_cast_kernel<VT, 2, 4><<<g, threads, 0, st>>>(pp, n_in, n_out, ub, ue); break;
+        case 4: fda_peer_reduce_cast_kernel<VT, 4, 2><<<g, threads, 0, st>>>(pp, n_in, n_out, ub, ue); break;
+        case 8: fda_peer_reduce_cast_kernel<VT, 8, 1><<<g, threads, 0, st>>>(pp, n_in, n_out, ub, ue); break;
+        default: fda_peer_reduce_cast_kernel<VT, 0, 1><<<g, threads, 0, st>>>(pp, n_in, n_out, ub, ue); break;
     }
     return cudaGetLastError();
 }
@@ -263,8 +264,7 @@ template <typename VT>
 cudaError_t launch_multimem(const float *mc_image, void *mc_out, size_t ub, size_t ue, cudaStream_t st) {
     const size_t units = ue - ub;
     if (units == 0) return cudaSuccess;
-    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 32);
-    if (max_blocks < 1) max_blocks = 1;
+    const int max_blocks = fda::config().peer_reduce_blocks;
     const int threads = 512;
     size_t blocks = (units + threads - 1) / threads;
     if (blocks > (size_t)max_blocks) blocks = (size_t)max_blocks;
@@ -288,7 +288,7 @@ extern "C" int fda_multimem_reduce_cast(const float *mc_image, void *mc_output, 
     if (value_dtype == FDA_DTYPE_F32) e = launch_multimem<float>(mc_image, mc_output, ub, ue, st);
     else if (value_dtype == FDA_DTYPE_F16) e = launch_multimem<__half>(mc_image, mc_output, ub, ue, st);
     else e = launch_multimem<__nv_bfloat16>(mc_image, mc_output, ub, ue, st);
-    return e == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
+    return status_of(e);
 }
 
 extern "C" int fda_peer_push_partials(const float *image, float *const *peer_staging, size_t slot_stride_elements,
@@ -313,8 +313,7 @@ extern "C" int fda_peer_push_partials(const float *image, float *const *peer_sta
         if (len > longest) longest = len;
     }
     if (longest == 0) return FDA_OK;
-    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 32);
-    if (max_blocks < 1) max_blocks = 1;
+    const int max_blocks = fda::config().peer_reduce_blocks;
     int bx = max_blocks / (world - 1);
     if (bx < 1) bx = 1;
     const size_t want = (longest + 511) / 512;
@@ -322,7 +321,7 @@ extern "C" int fda_peer_push_partials(const float *image, float *const *peer_sta
     const dim3 grid((unsigned)bx, (unsigned)(world - 1), 1);
     fda_peer_push_kernel<4><<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(image, pp, world,
                                                                                 (size_t)rank * slot_stride_elements);
-    return cudaGetLastError() == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
+    return status_of(cudaGetLastError());
 }
 
 extern "C" int fda_peer_reduce_staged_cast(const float *image, const float *staging, size_t slot_stride_elements,
@@ -344,8 +343,7 @@ extern "C" int fda_peer_reduce_staged_cast(const float *image, const float *stag
     const size_t ub = units * (size_t)rank / world, ue = units * (size_t)(rank + 1) / world;
     if (ue == ub) return FDA_OK;
     if ((ue - ub) * 8 > slot_stride_elements) return FDA_ERR_BAD_SHAPE;
-    int max_blocks = env_int("FDA_PEER_REDUCE_BLOCKS", 32);
-    if (max_blocks < 1) max_blocks = 1;
+    const int max_blocks = fda::config().peer_reduce_blocks;
     size_t blocks = (ue - ub + 511) / 512;
     if (blocks > (size_t)max_blocks) blocks = (size_t)max_blocks;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -356,31 +354,43 @@ extern "C" int fda_peer_reduce_staged_cast(const float *image, const float *stag
         fda_peer_reduce_staged_kernel<__half, 1><<<g, 512, 0, st>>>(image, staging, slot_stride_elements, pp, world, rank, ub, ue);
     else
         fda_peer_reduce_staged_kernel<__nv_bfloat16, 1><<<g, 512, 0, st>>>(image, staging, slot_stride_elements, pp, world, rank, ub, ue);
-    return cudaGetLastError() == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
+    return status_of(cudaGetLastError());
 }
 
-extern "C" int fda_peer_reduce_cast(const float *const *peer_images, void *const *peer_outputs, int world, int rank,
-                                    size_t num_elements, int value_dtype, void *stream) {
-    if (!peer_images || !peer_outputs) return FDA_ERR_NULL_POINTER;
+extern "C" int fda_group_reduce_cast(const float *const *group_images, int group_size, int group_rank,
+                                     void *const *peer_outputs, int world, int rank,
+                                     size_t num_elements, int value_dtype, void *stream) {
+    if (!group_images || !peer_outputs) return FDA_ERR_NULL_POINTER;
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return FDA_ERR_BAD_SHAPE;
+    if (group_size < 1 || group_size > world || group_rank < 0 || group_rank >= group_size) return FDA_ERR_BAD_SHAPE;
     if (value_dtype < 0 || value_dtype > 2) return FDA_ERR_BAD_DTYPE;
     if (num_elements % 8 != 0) return FDA_ERR_BAD_SHAPE;
     PeerPtrs pp;
     for (int p = 0; p < kMaxPeers; ++p) { pp.img[p] = nullptr; pp.out[p] = nullptr; }
+    for (int p = 0; p < group_size; ++p) {
+        const int r = (group_rank + p) % group_size;  // start with the local image, then walk the group's ring
+        if (!group_images[r]) return FDA_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(group_images[r]) & 15u) return FDA_ERR_MISALIGNED;
+        pp.img[p] = group_images[r];
+    }
     for (int p = 0; p < world; ++p) {
-        const int r = (rank + p) % world;  // start with the local copy, then walk the ring
-        if (!peer_images[r] || !peer_outputs[r]) return FDA_ERR_NULL_POINTER;
-        if ((reinterpret_cast<uintptr_t>(peer_images[r]) & 15u) || (reinterpret_cast<uintptr_t>(peer_outputs[r]) & 15u))
-            return FDA_ERR_MISALIGNED;
-        pp.img[p] = peer_images[r];
+        const int r = (rank + p) % world;  // local copy first
+        if (!peer_outputs[r]) return FDA_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(peer_outputs[r]) & 15u) return FDA_ERR_MISALIGNED;
         pp.out[p] = peer_outputs[r];
     }
     const size_t units = num_elements / 8;
-    const size_t ub = units * (size_t)rank / world, ue = units * (size_t)(rank + 1) / world;
+    const size_t ub = units * (size_t)group_rank / group_size, ue = units * (size_t)(group_rank + 1) / group_size;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    if (value_dtype == FDA_DTYPE_F32) e = launch<float>(pp, world, ub, ue, st);
-    else if (value_dtype == FDA_DTYPE_F16) e = launch<__half>(pp, world, ub, ue, st);
-    else e = launch<__nv_bfloat16>(pp, world, ub, ue, st);
-    return e == cudaSuccess ? FDA_OK : FDA_ERR_CUDA;
+    if (value_dtype == FDA_DTYPE_F32) e = launch<float>(pp, group_size, world, ub, ue, st);
+    else if (value_dtype == FDA_DTYPE_F16) e = launch<__half>(pp, group_size, world, ub, ue, st);
+    else e = launch<__nv_bfloat16>(pp, group_size, world, ub, ue, st);
+    return status_of(e);
+}
+
+extern "C" int fda_peer_reduce_cast(const float *const *peer_images, void *const *peer_outputs, int world, int rank,
+                                    size_t num_elements, int value_dtype, void *stream) {
+    // every rank holds a partial image: the group is the whole job
+    return fda_group_reduce_cast(peer_images, world, rank, peer_outputs, world, rank, num_elements, value_dtype, stream);
 }

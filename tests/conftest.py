@@ -14,6 +14,21 @@ if ROOT not in sys.path:
 GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
 
 
+def _inject_reference_debug_function():
+    """The reference package also exports its PyTorch implementation, ``ms_deform_attn_core_pytorch_3d``, and
+    its tests import it from ``ops3d``.  The product package deliberately ships no PyTorch implementation of
+    the operator; for the tests the CPU oracle's restatement is attached under the reference's names."""
+    import ops3d
+    import ops3d.flash_deform_attn
+    from oracle.fda_oracle import ms_deform_attn_core_pytorch_3d
+
+    ops3d.ms_deform_attn_core_pytorch_3d = ms_deform_attn_core_pytorch_3d
+    ops3d.flash_deform_attn.ms_deform_attn_core_pytorch_3d = ms_deform_attn_core_pytorch_3d
+
+
+_inject_reference_debug_function()
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
@@ -40,3 +55,30 @@ def load_golden(name):
     sizes = d["shapes"].prod(1)
     d["lsi"] = torch.cat((sizes.new_zeros(1), sizes.cumsum(0)[:-1]))
     return d
+
+
+@pytest.fixture
+def fda_env():
+    """``fda_env(NAME="value", ...)`` sets ``FDA_*`` knobs for one test and makes the library re-read them
+    (it reads its environment once, when loaded); everything is restored afterwards."""
+    from ops3d_b200 import capi
+
+    saved = {}
+
+    def set_knobs(**knobs):
+        for name, val in knobs.items():
+            if name not in saved:
+                saved[name] = os.environ.get(name)
+            if val is None:
+                os.environ.pop(name, None)
+            else:
+                os.environ[name] = str(val)
+        capi.reload_config()
+
+    yield set_knobs
+    for name, old in saved.items():
+        if old is None:
+            os.environ.pop(name, None)
+        else:
+            os.environ[name] = old
+    capi.reload_config()

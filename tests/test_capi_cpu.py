@@ -57,13 +57,20 @@ def test_forward_argument_validation_happens_on_the_host():
 
 def test_backward_workspace_contract():
     lib = capi.load()
-    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 50, 4, 0) == 0    # fp32 accumulates in place
-    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 50, 4, 2) == 2 * 100 * 8 * 32 * 4
-    assert lib.fda_backward_scratch_bytes(2, 100, 8, 32, 50, 4) == 0         # image fits L2: no binning
+    # arguments: B, N, G, D, L, Q, K, value dtype, packed dtype (0 = f32, 1 = f16, 2 = bf16)
+    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 2, 50, 4, 0, 0) == 0    # fp32 accumulates in place
+    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 2, 50, 4, 2, 0) == 2 * 100 * 8 * 32 * 4
+    assert lib.fda_backward_workspace_bytes(2, 100, 8, 32, 2, 50, 4, 2, 2) == 2 * 100 * 8 * 32 * 4  # no hand-over: no plane
+    assert lib.fda_backward_scratch_bytes(2, 100, 8, 32, 2, 50, 4, 0) == 0         # image fits L2: no binning
+    # 16-bit offsets: fp32 plane [B][Q*G][L*K] for the logit gradients handed from launch to launch
+    assert lib.fda_backward_scratch_bytes(2, 100, 8, 32, 2, 50, 4, 2) == 2 * 50 * 8 * 2 * 4 * 4
     # image of one batch element (598016 x 256 x 4 B) exceeds L2: counters + one 8-byte entry per (row, point)
-    big = lib.fda_backward_scratch_bytes(2, 598016, 8, 32, 1000, 8)
+    big = lib.fda_backward_scratch_bytes(2, 598016, 8, 32, 3, 1000, 8, 0)
     assert big == 3 * 2 * 64 * 4 + 2 * 1000 * 8 * 8 * 8
-    assert lib.fda_backward_workspace_bytes(2, 598016, 8, 32, 1000, 8, 2) == 2 * 598016 * 256 * 4 + big
+    assert lib.fda_backward_workspace_bytes(2, 598016, 8, 32, 3, 1000, 8, 2, 0) == 2 * 598016 * 256 * 4 + big
+    plane = 2 * 1000 * 8 * 3 * 8 * 4
+    assert lib.fda_backward_scratch_bytes(2, 598016, 8, 32, 3, 1000, 8, 2) == big + plane
+    assert lib.fda_backward_workspace_bytes(2, 598016, 8, 32, 3, 1000, 8, 2, 2) == 2 * 598016 * 256 * 4 + big + plane
     p = ctypes.c_void_p(16)
     args = (1, 8, 1, 8, 1, 1, 4, 2, 0, 64, 1, 0, None)
     assert lib.fda_backward(p, p, p, p, p, p, p, None, 0, *args) == 8        # workspace missing

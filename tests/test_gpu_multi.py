@@ -31,47 +31,60 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, mode, ret):
+def _worker(rank, world, port, mode, batch, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
                       FDA_SHARDED_REDUCE="nccl" if mode == "nccl" else "peer",
-                      FDA_PEER_REDUCE_MODE="auto" if mode in ("nccl", "slab-pipeline") else mode)
+                      FDA_PEER_REDUCE_MODE=mode if mode in ("p2p", "push", "multimem") else "auto",
+                      # the multicast and posted-store exchanges sum over all ranks: they need every rank on every image
+                      FDA_PARTITION="queries" if mode in ("push", "multimem", "queries") else "auto")
     if mode == "slab-pipeline":  # force the slab-binned backward and its slab-group exchange on this small problem
         os.environ.update(FDA_L2_KEEP_FRACTION="0.00001", FDA_BIN_SLAB_MB="0.25", FDA_SLAB_PARTS="3")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        from ops3d_b200 import FlashDeformAttnFunction
-        from ops3d_b200.sharded import shard_queries, sharded_flash_deform_attn
+        from ops3d_b200 import FlashDeformAttnFunction, capi
+        from ops3d_b200.sharded import partition, shard_rows, sharded_flash_deform_attn
 
+        capi.reload_config()
         shapes = [(8, 16, 32), (4, 8, 16)]
         K = 4
-        value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, 2, 301, 8, 32, K, seed=31)
+        value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, batch, 301, 8, 32, K, seed=31)
+        part = partition(batch, 301, rank, world)
         sh, lsi = sh.to(dev), lsi.to(dev)
         ok = True
         for step in range(2):  # twice: buffers of the first backward are reused by the second
             v = value.to(dev, torch.bfloat16).requires_grad_(True)
-            pk = shard_queries(packed, rank, world).to(dev).requires_grad_(True)
-            out = sharded_flash_deform_attn(v, sh, lsi, pk, 64, K)
-            out.backward(shard_queries(grad_out, rank, world).to(dev, torch.bfloat16))
+            pk = shard_rows(packed, part).to(dev).requires_grad_(True)
+            out = sharded_flash_deform_attn(v, sh, lsi, pk, 64, K, None, None, part)
+            out.backward(shard_rows(grad_out, part).to(dev, torch.bfloat16))
             v1 = value.to(dev, torch.bfloat16).requires_grad_(True)
             pk1 = packed.to(dev).requires_grad_(True)
             out1 = FlashDeformAttnFunction.apply(v1, sh, lsi, pk1, 64, K, True)
             out1.backward(grad_out.to(dev, torch.bfloat16))
             torch.cuda.synchronize()
             scale = v1.grad.float().abs().max().item()
-            ok &= torch.equal(out, shard_queries(out1, rank, world))
+            ok &= torch.equal(out, shard_rows(out1, part))
             ok &= (v.grad.float() - v1.grad.float()).abs().max().item() <= 2e-2 * scale
-            ok &= torch.equal(pk.grad, shard_queries(pk1.grad, rank, world))
-        ret[rank] = bool(ok)
+            ok &= torch.equal(pk.grad, shard_rows(pk1.grad, part))
+        # and against the CPU oracle, so the check does not rest on the single-GPU path alone
+        _, ref_gv, _ = fda_oracle.fused_forward_backward(value.bfloat16(), sh.cpu(), packed, grad_out.bfloat16(), K)
+        ok &= (v.grad.float().cpu() - ref_gv).abs().max().item() <= 2e-2 * ref_gv.abs().max().item()
+        ret[rank] = (bool(ok), part.kind)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["p2p", "push", "multimem", "nccl", "slab-pipeline"])
-def test_two_gpus_sharded_equals_unsharded(mode):
+# mode, batch size -> partition kind with two ranks
+CASES = [("p2p", 2, "batch"), ("p2p", 1, "batch-groups"), ("queries", 2, "queries"), ("push", 2, "queries"),
+         ("multimem", 2, "queries"), ("nccl", 2, "batch"), ("nccl", 1, "batch-groups"), ("slab-pipeline", 2, "batch"),
+         ("slab-pipeline", 1, "batch-groups")]
+
+
+@pytest.mark.parametrize("mode,batch,kind", CASES)
+def test_two_gpus_sharded_equals_unsharded(mode, batch, kind):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     ret = mp.get_context("spawn").Manager().dict()
-    mp.spawn(_worker, args=(2, _free_port(), mode, ret), nprocs=2, join=True)
-    assert dict(ret) == {0: True, 1: True}
+    mp.spawn(_worker, args=(2, _free_port(), mode, batch, ret), nprocs=2, join=True)
+    assert dict(ret) == {0: (True, kind), 1: (True, kind)}

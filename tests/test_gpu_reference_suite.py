@@ -1,14 +1,17 @@
 """The reference's own GPU test recipes (tests/test_flash_deform_attn.py, _stress.py and _wrapper.py
 of cell-observatory/ops3d) re-stated against this package: same shapes, seeds, value
 distributions and tolerances (rtol 1e-2 / atol 1e-3; bf16 atol 1e-2), same entry points
-(``FlashDeformAttnFunction.apply`` and the raw ``_C`` binding)."""
+(``FlashDeformAttnFunction.apply`` and the raw ``_C`` binding), and the reference's own import lines
+(tests/test_flash_deform_attn.py:9-12, tests/test_flash_deform_attn_wrapper.py:12-13):
+``ms_deform_attn_core_pytorch_3d`` is attached to ``ops3d`` by tests/conftest.py from the CPU oracle."""
 import pytest
 import torch
 import torch.nn.functional as F
 
-from oracle.fda_oracle import level_start_index_of, ms_deform_attn_core_pytorch_3d
-from ops3d_b200 import FlashDeformAttnFunction, _C
-from ops3d_b200.flash_deform_attn import findspec, findspec_bwd
+from ops3d import FlashDeformAttnFunction, ms_deform_attn_core_pytorch_3d
+from ops3d import _C as _C
+from ops3d.flash_deform_attn import findspec, findspec_bwd
+from oracle.fda_oracle import fused_forward_backward, level_start_index_of
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -43,10 +46,11 @@ def test_forward_half_default_shape():
 
 
 def test_backward_half_default_shape():
-    # reference default_backward_params scaled in Lq only (the value volume is kept): N=1, M=8, D=48,
-    # L=2 (64^3, 32^3), K=4; loss = out.sum() / 10
+    # reference default_backward_params (tests/conftest.py:60-87) at its own size: N=1, M=8, D=48,
+    # Lq = 64^3 + 32^3 = 294912, L=2 (64^3, 32^3), K=4; loss = out.sum() / 10, i.e. grad_output = 0.1.
+    # The oracle side is evaluated query-chunked (same autograd recipe per chunk) to bound host memory.
     shapes = [[64] * 3, [32] * 3]
-    N, M, D, L, K, Lq = 1, 8, 48, 2, 4, 16384
+    N, M, D, L, K, Lq = 1, 8, 48, 2, 4, 64 ** 3 + 32 ** 3
     sh = torch.tensor(shapes, dtype=torch.long, device=DEV)
     lsi = level_start_index_of(sh)
     S = int(sh.prod(1).sum())
@@ -58,19 +62,13 @@ def test_backward_half_default_shape():
     out = FlashDeformAttnFunction.apply(value, sh, lsi, packed, 64, K, True)
     (out.sum() / 10).backward()
 
-    v_ref = value.detach().float().cpu().requires_grad_(True)
-    loc_ref = loc.float().cpu().requires_grad_(True)
-    lg_ref = logits.float().cpu().requires_grad_(True)
-    soft = F.softmax(lg_ref.flatten(-2, -1), dim=-1).unflatten(-1, (L, K))
-    ref = ms_deform_attn_core_pytorch_3d(v_ref, sh.cpu(), loc_ref, soft)
-    (ref.sum() / 10).backward()
-
-    g_loc = packed.grad[..., : L * K * 3].reshape_as(loc).float().cpu()
-    g_att = packed.grad[..., L * K * 3:].reshape_as(logits).float().cpu()
+    ref, ref_gv, ref_gp = fused_forward_backward(value.detach().cpu(), sh.cpu(), packed.detach().cpu(),
+                                                 torch.full((N, Lq, M * D), 0.1), K, chunk=32768)
     assert torch.allclose(out.float().cpu(), ref, rtol=1e-2, atol=1e-3)
-    assert torch.allclose(value.grad.float().cpu(), v_ref.grad, rtol=1e-2, atol=1e-3)
-    assert torch.allclose(g_loc, loc_ref.grad, rtol=1e-2, atol=1e-3)
-    assert torch.allclose(g_att, lg_ref.grad, rtol=1e-2, atol=1e-3)
+    assert torch.allclose(value.grad.float().cpu(), ref_gv, rtol=1e-2, atol=1e-3)
+    g = packed.grad.float().cpu()
+    assert torch.allclose(g[..., : L * K * 3], ref_gp[..., : L * K * 3], rtol=1e-2, atol=1e-3)
+    assert torch.allclose(g[..., L * K * 3:], ref_gp[..., L * K * 3:], rtol=1e-2, atol=1e-3)
 
 
 @torch.no_grad()

@@ -40,6 +40,24 @@ def test_public_names():
     assert callable(FlashDeformAttnFunction.apply)
 
 
+def test_reference_import_lines_resolve():
+    """The import lines of the reference's callers and tests work unchanged (reference
+    tests/test_flash_deform_attn_wrapper.py:12-13, tests/test_extension.py:26-29,
+    tests/benchmark_flash_deform_attn.py:513)."""
+    import importlib
+
+    from ops3d import FlashDeformAttnFunction as F1
+    from ops3d import _C as C1
+    from ops3d.flash_deform_attn import FlashDeformAttnFunction as F2
+    from ops3d.flash_deform_attn import factors, findspec as fs, findspec_bwd as fsb
+
+    assert F1 is FlashDeformAttnFunction and F2 is FlashDeformAttnFunction
+    assert C1 is ops3d_b200._C and importlib.import_module("ops3d._C") is C1
+    assert hasattr(C1, "flash_deform_attn_forward") and hasattr(C1, "flash_deform_attn_backward")
+    assert fs is findspec and fsb is findspec_bwd
+    assert factors(12) == [1, 2, 3, 4, 6, 12] and factors(1) == [1] and factors(49) == [1, 7, 49]
+
+
 def _cpu_inputs(L=2, K=4, L_packed=None):
     shapes = torch.tensor([[4, 4, 4]] * L, dtype=torch.long)
     lsi = torch.cat((shapes.new_zeros(1), shapes.prod(1).cumsum(0)[:-1]))
@@ -67,9 +85,11 @@ def test_product_package_never_touches_the_oracle():
     import os
     import re
 
-    root = os.path.dirname(os.path.abspath(ops3d_b200.__file__))
+    import ops3d
+
     offenders = []
-    for dirpath, _, files in os.walk(root):
+    roots = [os.path.dirname(os.path.abspath(m.__file__)) for m in (ops3d_b200, ops3d)]
+    for root, (dirpath, _, files) in ((r, w) for r in roots for w in os.walk(r)):
         for name in files:
             if not name.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 continue

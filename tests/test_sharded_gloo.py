@@ -1,4 +1,4 @@
-"""World-size-2 check (gloo, CPU) of the query-sharding logic and of the one exchange step of the
+"""World-size-2 check (gloo, CPU) of the row-partitioning logic and of the one exchange step of the
 backward pass.  The per-rank operator is injected: here the CPU oracle stands in for the CUDA
 kernels, so what is under test is the host logic -- ranges, the all-reduce, the cast, gradient
 plumbing -- not the arithmetic."""
@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import fda_oracle
-from ops3d_b200.sharded import query_range, shard_queries, sharded_flash_deform_attn
+from ops3d_b200.sharded import partition, query_range, shard_queries, shard_rows, sharded_flash_deform_attn
 
 
 class OracleLocalOps:
@@ -46,31 +46,59 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, ret):
+@pytest.mark.parametrize("B,Q,world,kind", [(2, 598016, 1, "queries"), (2, 598016, 2, "batch"), (2, 598016, 4, "batch-groups"),
+                                             (2, 598016, 8, "batch-groups"), (4, 200, 2, "batch"), (1, 73728, 8, "batch-groups"),
+                                             (3, 100, 2, "queries"), (2, 10, 3, "queries")])
+def test_partition_tiles_the_rows_and_groups_share_one_batch_element(B, Q, world, kind):
+    parts = [partition(B, Q, r, world, mode="auto") for r in range(world)]
+    assert all(p.kind == kind for p in parts)
+    covered = torch.zeros(B, Q, dtype=torch.int32)
+    for r, p in enumerate(parts):
+        covered[p.b_begin:p.b_end, p.q_begin:p.q_end] += 1
+        assert p.group[p.group_rank] == r
+        # the ranks of a group work on the same batch elements and no others do
+        for other, q in enumerate(parts):
+            shares = (q.b_begin, q.b_end) == (p.b_begin, p.b_end)
+            assert shares == (other in p.group)
+        assert p.b_end - p.b_begin == parts[0].b_end - parts[0].b_begin  # same image count on every rank
+    assert bool((covered == 1).all())
+    if kind != "queries":
+        assert all(p.b_end - p.b_begin == max(1, B // world) for p in parts)
+    forced = [partition(B, Q, r, world, mode="queries") for r in range(world)]
+    assert all(p.kind == "queries" and (p.b_begin, p.b_end) == (0, B) for p in forced)
+    with pytest.raises(ValueError):
+        partition(B, Q, world, world)
+
+
+def _worker(rank, world, port, case, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         torch.set_num_threads(1)
+        B, mode = case
         shapes = [(4, 6, 8), (2, 3, 4)]
-        value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, 2, 13, 2, 8, 4, seed=9)
+        value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, B, 13, 2, 8, 4, seed=9)
+        part = partition(B, 13, rank, world, mode=mode)
         v = value.clone().requires_grad_(True)
-        pk = shard_queries(packed, rank, world).requires_grad_(True)
-        out = sharded_flash_deform_attn(v, sh, lsi, pk, 64, 4, None, OracleLocalOps())
-        out.backward(shard_queries(grad_out, rank, world))
+        pk = shard_rows(packed, part).requires_grad_(True)
+        out = sharded_flash_deform_attn(v, sh, lsi, pk, 64, 4, None, OracleLocalOps(), part)
+        out.backward(shard_rows(grad_out, part))
         ref_out, ref_gv, ref_gp = fda_oracle.fused_forward_backward(value, sh, packed, grad_out, 4)
-        ok = torch.allclose(out, shard_queries(ref_out, rank, world), atol=1e-5)
+        ok = torch.allclose(out, shard_rows(ref_out, part), atol=1e-5)
         ok &= torch.allclose(v.grad, ref_gv, atol=1e-4)  # reduced over ranks: the full gradient on every rank
-        ok &= torch.allclose(pk.grad, shard_queries(ref_gp, rank, world), atol=1e-4)
-        ret[rank] = bool(ok)
+        ok &= torch.allclose(pk.grad, shard_rows(ref_gp, part), atol=1e-4)
+        ret[rank] = (bool(ok), part.kind)
     finally:
         dist.destroy_process_group()
 
 
-def test_two_ranks_reproduce_the_unsharded_result():
+@pytest.mark.parametrize("case,kind", [((2, "auto"), "batch"), ((1, "auto"), "batch-groups"), ((2, "queries"), "queries"),
+                                       ((3, "auto"), "queries")])
+def test_two_ranks_reproduce_the_unsharded_result(case, kind):
     world = 2
     ret = mp.get_context("spawn").Manager().dict()
-    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
-    assert dict(ret) == {0: True, 1: True}
+    mp.spawn(_worker, args=(world, _free_port(), case, ret), nprocs=world, join=True)
+    assert dict(ret) == {0: (True, kind), 1: (True, kind)}
 
 
 def test_slab_plan_and_exchange_ranges_tile_the_image():
