@@ -52,6 +52,42 @@ struct RowGrad {
             s[r][0] = f.x; s[r][1] = f.y; s[r][2] = f.z; s[r][3] = f.w;
         }
     }
+    // Two-step form of the loads above, so that a caller can issue the loads of its NEXT row early and convert
+    // them when that row's turn comes: raw bits of the gather channels and of the scatter channels.
+    struct Raw {
+        uint4 d;
+        uint4 s[NRED];
+    };
+    static __device__ __forceinline__ Raw issue(const VT *go_row, int lane_c, int lpg, bool active, uint64_t pol) {
+        Raw r;
+        r.d = make_uint4(0u, 0u, 0u, 0u);
+        if (active) r.d = ldg16_hint(go_row + (size_t)lane_c * CPL, pol);
+#pragma unroll
+        for (int i = 0; i < NRED; ++i) {
+            r.s[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (active) r.s[i] = load4_raw<VT>(go_row + i * 4 * lpg + 4 * lane_c);
+        }
+        return r;
+    }
+    static __device__ __forceinline__ Raw issue_paired(const VT *go_own, int lane_c, bool active, const VT *go_even,
+                                                       const VT *go_odd, int tl, uint64_t pol) {
+        Raw r;
+        r.d = make_uint4(0u, 0u, 0u, 0u);
+        if (active) r.d = ldg16_hint(go_own + (size_t)lane_c * CPL, pol);
+#pragma unroll
+        for (int i = 0; i < NRED; ++i) r.s[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (go_even) r.s[0] = load4_raw<VT>(go_even + 4 * tl);
+        if (go_odd) r.s[NRED - 1] = load4_raw<VT>(go_odd + 4 * tl);
+        return r;
+    }
+    __device__ __forceinline__ void take(const Raw &r) {
+        Vec16<VT>::unpack(r.d, d);
+#pragma unroll
+        for (int i = 0; i < NRED; ++i) {
+            const float4 f = cvt4<VT>(r.s[i]);
+            s[i][0] = f.x; s[i][1] = f.y; s[i][2] = f.z; s[i][3] = f.w;
+        }
+    }
     // Paired layout (two rows of 4 lanes form a team of 8): s[0] = channels 4*tl.. of the EVEN row of the
     // team, s[1] = the same channels of the ODD row, tl = lane within the team.  `go_even` / `go_odd` may be
     // null when that row does not exist.
@@ -92,9 +128,10 @@ __device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, floa
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
         in[n] = active && pg.zin[n >> 2] && pg.yin[(n >> 1) & 1] && pg.xin[n & 1];
-        raw[n] = in[n] ? ldg16_hint(lvl + pg.off[n], pol_v) : make_uint4(0u, 0u, 0u, 0u);
+        raw[n] = in[n] ? ldg16_hint_ordered(lvl + pg.off[n], pol_v) : make_uint4(0u, 0u, 0u, 0u);
     }
-    float dot[8];
+    // Scatter first: the reductions depend on the weights and on grad_out only, so they are on their way to L2
+    // while the eight gathers above are still in flight; the dot products below are the first use of the gathers.
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
         const float w = (pg.wx[n & 1] * pg.wy[(n >> 1) & 1]) * pg.wz[n >> 2];
@@ -119,6 +156,10 @@ __device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, floa
             for (int r = 0; r < NRED; ++r)
                 red_add_f32x4_hint(dst + r * red_stride, aw * go.s[r][0], aw * go.s[r][1], aw * go.s[r][2], aw * go.s[r][3], pol_g);
         }
+    }
+    float dot[8];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
         float v[CPL];
         Vec16<VT>::unpack(raw[n], v);
 #ifdef FDA_NO_FFMA2

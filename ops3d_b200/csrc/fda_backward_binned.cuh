@@ -233,9 +233,10 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
     const int red_stride = 4 * p.lpg;
     const int lvl_first = plan.level * K;  // index of the level's first point inside a row
 
-    // Software pipeline over this group's entries: the entry is fetched two iterations ahead and its
-    // coordinates one iteration ahead, so that the dependent chain entry -> coordinates -> corner
-    // gathers costs one memory latency per iteration instead of three.
+    // Software pipeline over this group's entries: the entry is fetched two iterations ahead, its
+    // coordinates and its grad_out rows one iteration ahead, so that the dependent chain entry ->
+    // coordinates / grad_out -> corner gathers costs one memory latency per iteration instead of three,
+    // and the reductions (which need grad_out but not the gathers) go out while the gathers are in flight.
     const unsigned int step = gridDim.x * groups_per_block;
     const unsigned int first = blockIdx.x * groups_per_block + (tid >> p.gs_log2);
     const PT *packed_b = static_cast<const PT *>(p.packed) + (size_t)b * p.rows_per_b * (size_t)(4 * LK) + 3 * lvl_first;
@@ -248,13 +249,32 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
             x = load1<PT>(pc); y = load1<PT>(pc + 1); z = load1<PT>(pc + 2);
         }
     };
+    // grad_out rows of an entry (own row for the dot products; for the paired scatter the team's even and odd
+    // rows, whose pointers the two halves of a team exchange by shuffle).  Must be called by all 32 lanes.
+    const VT *go_base = static_cast<const VT *>(p.grad_out) + (size_t)b * p.rows_per_b * (size_t)p.D;
+    auto issue_go = [&](const uint2 &ent, bool have) -> typename RowGrad<VT>::Raw {
+        const unsigned int row = ent.x / (unsigned int)K;
+        const VT *go_own = go_base + (size_t)row * (size_t)p.D;
+        const bool act = have && lane_c < p.lpg;
+        if (kPair) {
+            const unsigned long long mine = have ? reinterpret_cast<unsigned long long>(go_own) : 0ull;
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, 4);
+            const bool odd = ((tid & 31) >> 2) & 1;
+            return RowGrad<VT>::issue_paired(go_own, lane_c, act, reinterpret_cast<const VT *>(odd ? other : mine),
+                                             reinterpret_cast<const VT *>(odd ? mine : other), tid & 7, pol_stream);
+        }
+        return RowGrad<VT>::issue(go_own, lane_c, p.lpg, act, pol_stream);
+    };
     uint2 ent_cur = fetch_entry(first), ent_nxt = fetch_entry(first + step);
     float x, y, z;
     fetch_coords(ent_cur, first < count, x, y, z);
+    typename RowGrad<VT>::Raw go_raw = issue_go(ent_cur, first < count);
     for (unsigned int e = first, base = blockIdx.x * groups_per_block; base < count; base += step, e += step) {
+        // one iteration ahead: coordinates and grad_out rows of the next entry; two ahead: the entry itself
         const uint2 ent_nn = fetch_entry(e + 2 * step);
         float xn, yn, zn;
         fetch_coords(ent_nxt, e + step < count, xn, yn, zn);
+        const typename RowGrad<VT>::Raw go_raw_nxt = issue_go(ent_nxt, e + step < count);
         const bool have = e < count;
         const int row = (int)(ent_cur.x / (unsigned int)K);
         const int k = (int)(ent_cur.x - (unsigned int)row * (unsigned int)K);
@@ -266,21 +286,15 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
         const VT *lvl = static_cast<const VT *>(p.value) + head_elem + (size_t)lane_c * CPL;
         float *acc_lvl = p.accum + head_elem + (size_t)lane_c * 4;
         RowGrad<VT> go;
-        const VT *go_own = static_cast<const VT *>(p.grad_out) + grow * (size_t)p.D;
+        go.take(go_raw);
         float *acc_even = nullptr, *acc_odd = nullptr;
         if (kPair) {
-            // the partner entry of this lane's team is an arbitrary other row: exchange row pointers by shuffle
-            const unsigned long long mine_go = have ? reinterpret_cast<unsigned long long>(go_own) : 0ull;
+            // the partner entry of this lane's team is an arbitrary other row: exchange image bases by shuffle
             const unsigned long long mine_acc = reinterpret_cast<unsigned long long>(p.accum + head_elem);
-            const unsigned long long other_go = __shfl_xor_sync(0xffffffffu, mine_go, 4);
             const unsigned long long other_acc = __shfl_xor_sync(0xffffffffu, mine_acc, 4);
             const bool odd = ((tid & 31) >> 2) & 1;
-            go.load_paired(go_own, lane_c, active, reinterpret_cast<const VT *>(odd ? other_go : mine_go),
-                           reinterpret_cast<const VT *>(odd ? mine_go : other_go), tid & 7, pol_stream);
             acc_even = reinterpret_cast<float *>(odd ? other_acc : mine_acc);
             acc_odd = reinterpret_cast<float *>(odd ? mine_acc : other_acc);
-        } else {
-            go.load(go_own, lane_c, p.lpg, active, pol_stream);
         }
         float gx, gy, gz, da;
         point_backward<VT, kPair>(lv, p.GD, x, y, z, a, lvl, acc_lvl, go, red_stride, active, gs, pol_keep, pol_keep,
@@ -294,6 +308,7 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
         }
         ent_cur = ent_nxt; ent_nxt = ent_nn;
         x = xn; y = yn; z = zn;
+        go_raw = go_raw_nxt;
     }
 }
 

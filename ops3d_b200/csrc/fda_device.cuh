@@ -271,6 +271,39 @@ __device__ __forceinline__ uint4 ldg16_hint(const void *p, uint64_t pol) {
         : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p), "l"(pol));
     return r;
 }
+// The same load, kept in program order relative to the reductions that follow it (see point_backward).
+__device__ __forceinline__ uint4 ldg16_hint_ordered(const void *p, uint64_t pol) {
+    uint4 r;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p), "l"(pol));
+    return r;
+}
+// Four consecutive elements as raw bits (x, y used for 16-bit types), and their conversion to fp32.
+template <typename T> __device__ __forceinline__ uint4 load4_raw(const T *p);
+template <> __device__ __forceinline__ uint4 load4_raw<float>(const float *p) {
+    return __ldg(reinterpret_cast<const uint4 *>(p));
+}
+template <> __device__ __forceinline__ uint4 load4_raw<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2 *>(p));
+    return make_uint4(r.x, r.y, 0u, 0u);
+}
+template <> __device__ __forceinline__ uint4 load4_raw<__half>(const __half *p) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2 *>(p));
+    return make_uint4(r.x, r.y, 0u, 0u);
+}
+template <typename T> __device__ __forceinline__ float4 cvt4(const uint4 &r);
+template <> __device__ __forceinline__ float4 cvt4<float>(const uint4 &r) {
+    return make_float4(__uint_as_float(r.x), __uint_as_float(r.y), __uint_as_float(r.z), __uint_as_float(r.w));
+}
+template <> __device__ __forceinline__ float4 cvt4<__nv_bfloat16>(const uint4 &r) {
+    return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
+                       __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float4 cvt4<__half>(const uint4 &r) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
 // fp32 x4 reduction into global memory (one 16-byte L2 atomic operation, no return value).
 __device__ __forceinline__ void red_add_f32x4_hint(float *p, float a, float b, float c, float d, uint64_t pol) {
     asm volatile("red.global.add.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"

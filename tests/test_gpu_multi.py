@@ -88,3 +88,53 @@ def test_two_gpus_sharded_equals_unsharded(mode, batch, kind):
     ret = mp.get_context("spawn").Manager().dict()
     mp.spawn(_worker, args=(2, _free_port(), mode, batch, ret), nprocs=2, join=True)
     assert dict(ret) == {0: (True, kind), 1: (True, kind)}
+
+
+def _host_worker(rank, world, port, batch, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from ops3d_b200.host_stream import HostStreamedStep
+        from ops3d_b200.sharded import PeerReducer, partition, shard_rows
+
+        shapes = [(8, 16, 32), (4, 8, 16)]
+        K, Q, G, D = 4, 301, 8, 32
+        value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, batch, Q, G, D, K, seed=33)
+        part = partition(batch, Q, rank, world)
+        value_h = value.bfloat16().pin_memory()
+        packed_h = shard_rows(packed, part).pin_memory()
+        go_h = shard_rows(grad_out, part).bfloat16().pin_memory()
+        reducer = PeerReducer(value.shape, torch.bfloat16, dev, spatial_shapes=sh, part=part)
+        step = HostStreamedStep(value.shape, torch.bfloat16, packed_h.shape, torch.float32, K, sh.to(dev), lsi.to(dev), dev,
+                                chunk_queries=40, reducer=reducer)
+        out_h = torch.empty(packed_h.shape[0], packed_h.shape[1], G * D, dtype=torch.bfloat16).pin_memory()
+        gv_h = torch.zeros(value.shape, dtype=torch.bfloat16).pin_memory()
+        gp_h = torch.empty(packed_h.shape).pin_memory()
+        ref_out, ref_gv, ref_gp = fda_oracle.fused_forward_backward(value_h, sh, packed, grad_out.bfloat16(), K)
+        ok = True
+        for _ in range(2):  # twice: slots, events and the reducer's buffers are reused
+            gv_h.zero_()
+            f0, f1 = step.run(value_h, packed_h, go_h, out_h, gv_h, gp_h)
+            torch.cuda.synchronize()
+            ok &= (out_h.float() - shard_rows(ref_out, part)).abs().max().item() <= 2e-2 * ref_out.abs().max().item()
+            ok &= (gp_h - shard_rows(ref_gp, part)).abs().max().item() <= 2e-2 * ref_gp.abs().max().item()
+            # this rank downloaded its 1/world slice of the reduced grad_value; the device copy is complete on every rank
+            ok &= (gv_h.view(-1)[f0:f1].float() - ref_gv.view(-1)[f0:f1]).abs().max().item() <= 2e-2 * ref_gv.abs().max().item()
+            ok &= (reducer.out.float().cpu() - ref_gv).abs().max().item() <= 2e-2 * ref_gv.abs().max().item()
+            ok &= (f1 - f0) >= ref_gv.numel() // world - 8
+        ret[rank] = (bool(ok), part.kind)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("batch,kind", [(2, "batch"), (1, "batch-groups")])
+def test_two_gpus_host_streamed_step(batch, kind):
+    """Host buffers in, host buffers out, on two ranks: rows streamed in chunks, value slices all-gathered over
+    NVLink when two ranks share a batch element, images exchanged once per batch element; against the CPU oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_host_worker, args=(2, _free_port(), batch, ret), nprocs=2, join=True)
+    assert dict(ret) == {0: (True, kind), 1: (True, kind)}
