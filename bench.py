@@ -462,32 +462,71 @@ def run_ours(args, cfg):
         grad_value = torch.empty_like(value)
         accum = torch.empty(value.shape, dtype=torch.float32, device=dev) if (vdt != torch.float32 or world > 1) else grad_value
 
-    def step(ev=None):
-        nonlocal grad_value
-        if ev: ev[0].record()
+    def phase_forward():
         capi.forward(value_local, shapes, lsi, packed, K, out=out)
-        if ev: ev[1].record()
+
+    def phase_backward():
+        nonlocal grad_value
         if use_peer:
             # scatter on this stream, fused NVLink reduce+cast of finished pieces overlapped on a side stream
             grad_value, _ = reducer.backward(value, shapes, lsi, packed, grad_out, K, grad_packed=grad_packed)
-            if ev: ev[2].record(); ev[3].record()
             return
         if world > 1:
             accum.zero_()   # the batch elements other ranks work on contribute zeros to the sum
         capi.backward_accumulate_levels(value_local, shapes, lsi, packed, grad_out, K, accum[part.b_begin:part.b_end],
                                         grad_packed, 0, L, (0 if world > 1 else capi.BWD_ZERO_IMAGE) | capi.BWD_FINALIZE,
                                         scratch=scratch)
-        if ev: ev[2].record()
+
+    def phase_tail():
+        if use_peer:
+            return
         if world > 1:
             dist.all_reduce(accum)
         if accum is not grad_value:
             capi.cast_grad_value(accum, grad_value)
+
+    phases = [phase_forward, phase_backward, phase_tail]
+
+    def step(ev=None):
+        for i, phase in enumerate(phases):
+            if ev: ev[i].record()
+            phase()
         if ev: ev[3].record()
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
+
+    # Launch-bound configurations (a step of a few launches that each take microseconds) are replayed from CUDA
+    # graphs, so that the device time is measured rather than the Python call overhead between launches.
+    use_graph = world == 1 and (args.graph == "on" or (args.graph == "auto" and args.config in (1, 2, 3)))
+    launches_per_step = None
+    whole_graph = None
+    if use_graph:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step()   # once more on the capture stream's side, so nothing is initialised during capture
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        n0 = capi.KERNEL_LAUNCHES
+        graphs = []
+        for phase in phases:
+            before = capi.KERNEL_LAUNCHES
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                phase()
+            graphs.append(g if capi.KERNEL_LAUNCHES > before else None)  # a phase without launches (no cast for fp32)
+        launches_per_step = capi.KERNEL_LAUNCHES - n0
+        whole_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(whole_graph):
+            for phase in (phase_forward, phase_backward, phase_tail):
+                phase()
+        phases = [(g.replay if g is not None else (lambda: None)) for g in graphs]
+        for _ in range(3):
+            step(); whole_graph.replay()
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
@@ -498,12 +537,20 @@ def run_ours(args, cfg):
     for ev in events:
         step(ev)
     torch.cuda.synchronize()
+    total_ms = events[0][0].elapsed_time(events[-1][3])
+    if whole_graph is not None:   # the step as ONE graph, replayed back to back: the step time proper
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0.record()
+        for _ in range(args.steps):
+            whole_graph.replay()
+        w1.record()
+        torch.cuda.synchronize()
+        total_ms = w0.elapsed_time(w1)
     t_host1 = time.perf_counter()
-    gpu_launches = capi.KERNEL_LAUNCHES - launches0
+    gpu_launches = capi.KERNEL_LAUNCHES - launches0 if launches_per_step is None else launches_per_step * args.steps
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
-    total_ms = events[0][0].elapsed_time(events[-1][3])
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in events) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in events) / args.steps
     tail_ms = sum(e[2].elapsed_time(e[3]) for e in events) / args.steps
@@ -620,6 +667,8 @@ def run_ours(args, cfg):
                            + ("; bytes are this rank's (each rank uploads its rows and its batch element(s) of value, "
                               "downloads its rows and 1/N of grad_value)" if world > 1 else "")},
             "gpu_launches": gpu_launches,
+            "launch": ("CUDA graph replay (ms_per_step: the whole step as one graph; per-phase times: one graph per phase)"
+                       if use_graph else "one C-ABI call per phase from Python"),
             "clocks": clocks,
         }
         if peer_note:
@@ -654,6 +703,8 @@ def main():
     ap.add_argument("--no-ref-cuda", action="store_true",
                     help="do not time the reference's own CUDA kernels (timed by default at N=1 when baseline/_ref/ops3d_ref_C.so exists)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="replay the step from CUDA graphs (auto: the launch-bound configurations 1-3, one GPU)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.batch or args.queries:

@@ -54,7 +54,7 @@ fda::Config read_config() {
     c.l2_keep_fraction = 0.7;
     c.binning = 1;
     c.bin_slab_mb = 16.0;  // 8-16 MB of image per slab measured best on B200 (value rows of the slab add half of that)
-    c.bin_grid_x = 592;    // 4 blocks per SM's worth of 2 resident blocks: each block strides over its slab's list
+    c.bin_grid_x = 0;      // blocks striding over one slab's list; 0: sized from the entry count (launch_binned_slabs)
     c.pair_rows = 1;
     c.forced_variant = 0;
     c.peer_reduce_blocks = 32;
@@ -63,7 +63,7 @@ fda::Config read_config() {
     if (const char *e = std::getenv("FDA_BINNING")) c.binning = std::atoi(e) != 0;
     if (const char *e = std::getenv("FDA_BIN_SLAB_MB")) c.bin_slab_mb = std::atof(e);
     if (const char *e = std::getenv("FDA_BIN_GRID_X")) c.bin_grid_x = std::atoi(e);
-    if (c.bin_grid_x < 1) c.bin_grid_x = 1;
+    if (c.bin_grid_x < 0) c.bin_grid_x = 0;
     if (const char *e = std::getenv("FDA_PAIR_ROWS")) c.pair_rows = std::atoi(e) != 0;
     if (const char *e = std::getenv("FDA_FORCE_VARIANT")) {
         if (!std::strcmp(e, "reg")) c.forced_variant = 1;
@@ -247,7 +247,18 @@ int launch_bin_prepare(const fda::Problem &p, cudaStream_t st) {
 template <typename VT, typename PT>
 int launch_binned_slabs(const fda::Problem &p, cudaStream_t st) {
     // x: blocks striding over one slab's list; y: slab (slabs run one after the other); z: batch element
-    const int gx = g_config.bin_grid_x;
+    // About 16 entries per lane group and slab measured best (full size: 592 / 1184 blocks 43.4 / 42.8 ms per
+    // backward; an eighth of the rows: 592 / 296 blocks 6.45 / 6.25 ms).  The host does not know the slab count
+    // (the shapes live on the device); it estimates it from the whole image, which the largest level dominates.
+    int gx = g_config.bin_grid_x;
+    if (gx <= 0) {
+        const unsigned long long image_bytes = (unsigned long long)p.N * p.GD * 4ull;
+        unsigned long long slabs = (image_bytes + p.bin_slab_bytes - 1) / p.bin_slab_bytes;
+        slabs = slabs < 2 ? 2 : (slabs > (unsigned long long)fda::kMaxSlabs ? fda::kMaxSlabs : slabs);
+        const unsigned long long groups_per_block = (unsigned long long)(fda::kThreads >> p.gs_log2);
+        unsigned long long want = p.bin_cap / slabs / (16ull * groups_per_block);
+        gx = (int)(want < 74 ? 74 : (want > 2368 ? 2368 : want));
+    }
     const dim3 grid((unsigned)gx, fda::kMaxSlabs, (unsigned)p.B);
     if (pair_rows<VT>(p)) fda::fda_backward_binned_kernel<VT, PT, true><<<grid, fda::kThreads, 0, st>>>(p);
     else fda::fda_backward_binned_kernel<VT, PT, false><<<grid, fda::kThreads, 0, st>>>(p);

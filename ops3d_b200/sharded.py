@@ -130,8 +130,8 @@ class PeerReducer:
     ``FDA_PEER_REDUCE_MODE=multimem|push`` select the NVSwitch-multicast and the posted-store variants.
     Pieces, when ``spatial_shapes`` is given: the largest pyramid level first (most of the bytes), the
     other levels second; and when that level is handled by the slab-binned kernels it is launched in
-    slab groups whose finished z-ranges are exchanged one by one (``FDA_SLAB_PARTS``; 4 groups from
-    4 ranks up, else 1).  Only the small remainder of the last batch element is exposed.
+    slab groups whose finished z-ranges are exchanged one by one (``FDA_SLAB_PARTS``, default one group:
+    the level as a whole).  Only the small remainder of the last batch element is exposed.
 
     All ranks must call ``backward`` with the same shapes: every rank issues the same sequence of
     barriers.  The schedule (slab plan, level passes) is agreed on across ranks with one small
@@ -235,10 +235,9 @@ class PeerReducer:
             plan = capi.bin_plan(self.shapes_host, one, packed.shape[1], K)
             if plan is not None:
                 # Slab groups per level: more groups start the exchange earlier but add launches and barriers.
-                # Measured: on 2 GPUs (exchange short against compute) 1 / 2 / 4 groups give 27.7 / 27.9 / 28.1 ms
-                # per step, on 8 GPUs 4 groups gave the shortest backward relative to the box's forward time.
-                default_parts = 4 if self.world >= 4 else 1
-                parts = max(1, int(os.environ.get("FDA_SLAB_PARTS", str(default_parts))))
+                # Measured with the batch-aligned partition on 8 GPUs (4 ranks per batch element): 1 / 2 / 4 / 8
+                # groups give 7.69 / 7.80 / 8.07 / 8.58 ms per step; on 2 GPUs 1 / 2 / 4 groups 27.7 / 27.9 / 28.1 ms.
+                parts = max(1, int(os.environ.get("FDA_SLAB_PARTS", "1")))
                 slab = slab_exchange_ranges(self.shapes_host, self.shape, plan, parts)
         if slab is not None:
             schedule = ("slabs", slab)
