@@ -273,6 +273,16 @@ int fda_pack_sampling(const void *offsets, const void *reference_points, const v
                       int num_levels, int num_points, int dtype, void *stream);
 
 /*
+ * Backward of fda_pack_sampling: from grad_packed [B,Lq,G,L*K*4] (fp32, as the operator's backward returns it
+ * for fp32 offsets) to grad_offsets [B,Lq,G,L,K,3] = coordinate gradients / (W_l,H_l,D_l),
+ * grad_reference_points [B,Lq,L,3] = coordinate gradients summed over heads and points, and
+ * grad_logits [B,Lq,G,L,K], all of `dtype`.  One fused pass.  No counterpart in the reference.
+ */
+int fda_pack_sampling_backward(const float *grad_packed, const int64_t *spatial_shapes, void *grad_offsets,
+                               void *grad_reference_points, void *grad_logits, int batch, int num_query,
+                               int num_heads, int num_levels, int num_points, int dtype, void *stream);
+
+/*
  * Backward pass that needs no workspace from the caller and allocates nothing: same inputs,
  * outputs and results as fda_backward, but the fp32 accumulation image sits in a fixed
  * FDA_NOALLOC_MAX_ELEMENTS-float (64 MiB) array inside the library, present on every GPU that

@@ -19,7 +19,7 @@ EXPORTS = (
     "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
     "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
-    "fda_pack_sampling", "fda_reload_config", "fda_group_reduce_cast",
+    "fda_pack_sampling", "fda_pack_sampling_backward", "fda_reload_config", "fda_group_reduce_cast",
 )
 BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE = 1, 2, 4, 8
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
@@ -76,6 +76,8 @@ def load() -> ctypes.CDLL:
     lib.fda_backward_binned_part.restype = i
     lib.fda_pack_sampling.argtypes = [vp] * 5 + [i] * 6 + [vp]
     lib.fda_pack_sampling.restype = i
+    lib.fda_pack_sampling_backward.argtypes = [vp] * 5 + [i] * 6 + [vp]
+    lib.fda_pack_sampling_backward.restype = i
     lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
     lib.fda_cast_grad_value.restype = i
     lib.fda_backward_noalloc.argtypes = [vp] * 7 + [i] * 10 + [vp]
@@ -318,3 +320,17 @@ def pack_sampling(offsets, reference_points, logits, shapes):
                                        packed.data_ptr(), B, Q, G, L, K, DTYPE_CODE[offsets.dtype], _stream(offsets)))
     _count(1)
     return packed
+
+
+def pack_sampling_backward(grad_packed, shapes, B, Q, G, L, K, dtype):
+    """``fda_pack_sampling_backward``: ``grad_packed`` fp32 ``[B,Q,G,L*K*4]`` -> ``(grad_offsets [B,Q,G,L,K,3],
+    grad_reference_points [B,Q,L,3], grad_logits [B,Q,G,L,K])`` in ``dtype``."""
+    dev = grad_packed.device
+    g_off = torch.empty(B, Q, G, L, K, 3, dtype=dtype, device=dev)
+    g_ref = torch.empty(B, Q, L, 3, dtype=dtype, device=dev)
+    g_logit = torch.empty(B, Q, G, L, K, dtype=dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(load().fda_pack_sampling_backward(grad_packed.data_ptr(), shapes.data_ptr(), g_off.data_ptr(), g_ref.data_ptr(),
+                                                g_logit.data_ptr(), B, Q, G, L, K, DTYPE_CODE[dtype], _stream(grad_packed)))
+    _count(1)
+    return g_off, g_ref, g_logit

@@ -53,7 +53,7 @@ fda::Config read_config() {
     fda::Config c;
     c.l2_keep_fraction = 0.7;
     c.binning = 1;
-    c.bin_slab_mb = 16.0;  // 8-16 MB of image per slab measured best on B200 (value rows of the slab add half of that)
+    c.bin_slab_mb = 4.0;   // image bytes per brick (value rows add half of that); 16 / 8 / 4 / 2 MB: 43.4 / 42.5 / 42.4 / 42.2 ms per backward
     c.bin_grid_x = 0;      // blocks striding over one slab's list; 0: sized from the entry count (launch_binned_slabs)
     c.pair_rows = 1;
     c.forced_variant = 0;

@@ -28,7 +28,7 @@
 
 namespace fda {
 
-// slab of a point from its normalised coordinates, or -1 when no corner lies inside the level
+// brick (z-slab * ny + y-part) of a point from its normalised coordinates, or -1 when no corner lies inside the level
 __device__ __forceinline__ int slab_of_point(const LevelGeom &lv, const BinPlan &plan, float x, float y, float z) {
     const float xf = floorf(unnormalize(x, (float)lv.W));
     const float yf = floorf(unnormalize(y, (float)lv.H));
@@ -37,9 +37,10 @@ __device__ __forceinline__ int slab_of_point(const LevelGeom &lv, const BinPlan 
     const bool ok = (xf >= -1.f) && (xf <= (float)(lv.W - 1)) && (yf >= -1.f) && (yf <= (float)(lv.H - 1)) &&
                     (zf >= -1.f) && (zf <= (float)(lv.D - 1));
     if (!ok) return -1;
-    int z0 = (int)zf;
+    int z0 = (int)zf, y0 = (int)yf;
     z0 = z0 < 0 ? 0 : z0;
-    return z0 / plan.depth;
+    y0 = y0 < 0 ? 0 : y0;
+    return (z0 / plan.depth) * plan.ny + y0 / plan.ydepth;
 }
 
 __device__ __forceinline__ LevelGeom level_geom_of(const Problem &p, int l) {
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(256) fda_bin_count_kernel(const Problem p) {
         plan = make_bin_plan(p);
         lv = level_geom_of(p, plan.level);
     }
-    if (threadIdx.x < kMaxSlabs) hist[threadIdx.x] = 0u;
+    for (int i = threadIdx.x; i < kMaxSlabs; i += blockDim.x) hist[i] = 0u;
     __syncthreads();
     if (!plan.enabled) return;
     const int b = blockIdx.y;
@@ -92,8 +93,8 @@ __global__ void __launch_bounds__(256) fda_bin_count_kernel(const Problem p) {
         }
     }
     __syncthreads();
-    if (threadIdx.x < plan.slabs && hist[threadIdx.x])
-        atomicAdd(p.bin_counters + (size_t)b * kMaxSlabs + threadIdx.x, hist[threadIdx.x]);
+    for (int i = threadIdx.x; i < plan.slabs * plan.ny; i += blockDim.x)
+        if (hist[i]) atomicAdd(p.bin_counters + (size_t)b * kMaxSlabs + i, hist[i]);
 }
 
 // counters: [0] counts, [1] offsets (exclusive scan per batch element), [2] cursors (zeroed by the host)
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(kThreads) fda_bin_fill_kernel(const Problem p)
         plan = make_bin_plan(p);
         lv = level_geom_of(p, plan.level);
     }
-    if (tid < kMaxSlabs) hist[tid] = 0u;
+    for (int i = tid; i < kMaxSlabs; i += blockDim.x) hist[i] = 0u;
     __syncthreads();
     if (!plan.enabled) return;
     const int b = blockIdx.y;
@@ -181,9 +182,9 @@ __global__ void __launch_bounds__(kThreads) fda_bin_fill_kernel(const Problem p)
         }
     }
     __syncthreads();
-    if (tid < plan.slabs) {
-        const unsigned int n = hist[tid];
-        base[tid] = n ? atomicAdd(p.bin_counters + (size_t)(2 * p.B + b) * kMaxSlabs + tid, n) : 0u;
+    for (int i = tid; i < plan.slabs * plan.ny; i += blockDim.x) {
+        const unsigned int n = hist[i];
+        base[i] = n ? atomicAdd(p.bin_counters + (size_t)(2 * p.B + b) * kMaxSlabs + i, n) : 0u;
     }
     __syncthreads();
     if (row_ok) {
@@ -212,7 +213,9 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_bin
     __syncthreads();
     const int b = blockIdx.z;
     if (!plan.enabled) return;
-    const int slab_first = plan.slabs * p.slab_part / p.slab_parts, slab_end = plan.slabs * (p.slab_part + 1) / p.slab_parts;
+    // slab groups are cut between z-slabs; each z-slab has plan.ny bricks with a list of their own
+    const int slab_first = (plan.slabs * p.slab_part / p.slab_parts) * plan.ny;
+    const int slab_end = (plan.slabs * (p.slab_part + 1) / p.slab_parts) * plan.ny;
     const int slab = slab_first + (int)blockIdx.y;
     if (slab >= slab_end) return;
     const LevelGeom lv = lv_s;

@@ -7,7 +7,7 @@ namespace fda {
 struct Config {
     double l2_keep_fraction;  // FDA_L2_KEEP_FRACTION  share of L2 that may be marked "evict last" (0.7)
     int binning;              // FDA_BINNING           0 switches the slab-binned backward off (1)
-    double bin_slab_mb;       // FDA_BIN_SLAB_MB       share of the fp32 image per slab (16)
+    double bin_slab_mb;       // FDA_BIN_SLAB_MB       bytes of the fp32 image per slab or brick, in MB (4)
     int bin_grid_x;           // FDA_BIN_GRID_X        blocks striding over one slab's list (0 = from the entry count)
     int pair_rows;            // FDA_PAIR_ROWS         0 switches the paired-row scatter off (1)
     int forced_variant;       // FDA_FORCE_VARIANT     0 library's choice, 1 "reg", 2 "smem" (forward staging)

@@ -70,18 +70,20 @@ struct Problem {
     float *dalpha;
 };
 
-constexpr int kMaxSlabs = 64;
+constexpr int kMaxSlabs = 128;
 
-// Which level (if any) is handled slab by slab, and how it is cut along z.  A pure function of the
-// shapes and launch parameters, so every kernel of one backward call -- and the host, when it has a
-// host copy of the shapes -- derives the same plan.
+// Which level (if any) is handled slab by slab, and how it is cut: along z into `slabs` slabs of `depth`
+// planes, and -- when a single plane is still larger than the target -- each slab along y into `ny` bricks
+// of `ydepth` rows.  Brick index = z-slab * ny + y-part; there are slabs * ny <= kMaxSlabs bricks.  A pure
+// function of the shapes and launch parameters, so every kernel of one backward call -- and the host, when
+// it has a host copy of the shapes -- derives the same plan.
 struct BinPlan {
-    int level, enabled, slabs, depth;
+    int level, enabled, slabs, depth, ny, ydepth;
 };
 __host__ __device__ inline BinPlan bin_plan_from(const int64_t *shapes, int L, int GD, unsigned long long l2_keep_bytes,
                                                  unsigned long long slab_bytes, int level_mask, int allowed) {
     BinPlan plan;
-    plan.level = 0; plan.enabled = 0; plan.slabs = 1; plan.depth = 1;
+    plan.level = 0; plan.enabled = 0; plan.slabs = 1; plan.depth = 1; plan.ny = 1; plan.ydepth = 1 << 30;
     if (!allowed) return plan;
     unsigned long long best = 0;
     for (int l = 0; l < L; ++l) {
@@ -89,7 +91,7 @@ __host__ __device__ inline BinPlan bin_plan_from(const int64_t *shapes, int L, i
         if (c > best) { best = c; plan.level = l; }
     }
     const unsigned long long image_bytes = best * (unsigned long long)GD * 4ull;
-    const int Dz = (int)shapes[3 * plan.level];
+    const int Dz = (int)shapes[3 * plan.level], H = (int)shapes[3 * plan.level + 1];
     if (!((level_mask >> plan.level) & 1) || image_bytes <= l2_keep_bytes || Dz < 2) return plan;
     unsigned long long want = (image_bytes + slab_bytes - 1) / slab_bytes;
     if (want > (unsigned long long)kMaxSlabs) want = kMaxSlabs;
@@ -97,6 +99,17 @@ __host__ __device__ inline BinPlan bin_plan_from(const int64_t *shapes, int L, i
     if (want < 2) want = 2;
     plan.depth = (Dz + (int)want - 1) / (int)want;
     plan.slabs = (Dz + plan.depth - 1) / plan.depth;
+    if (plan.depth == 1) {  // one plane per slab and possibly still too large: cut the planes along y
+        const unsigned long long plane_bytes = image_bytes / (unsigned long long)Dz;
+        unsigned long long ny = (plane_bytes + slab_bytes - 1) / slab_bytes;
+        const unsigned long long room = (unsigned long long)(kMaxSlabs / plan.slabs);
+        if (ny > room) ny = room;
+        if (ny > (unsigned long long)H) ny = H;
+        if (ny > 1) {
+            plan.ydepth = (H + (int)ny - 1) / (int)ny;
+            plan.ny = (H + plan.ydepth - 1) / plan.ydepth;
+        }
+    }
     plan.enabled = 1;
     return plan;
 }

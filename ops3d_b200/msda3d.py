@@ -27,7 +27,7 @@ from .flash_deform_attn import FlashDeformAttnFunction
 class PackSamplingFunction(Function):
     """``packed = pack(offsets, reference_points, logits, spatial_shapes)`` (fused CUDA kernel, fp32 output);
     gradients flow to ``offsets`` (divided by the level extent), ``reference_points`` (summed over heads
-    and points) and ``logits`` (unchanged)."""
+    and points) and ``logits`` (unchanged) through one fused CUDA kernel as well."""
 
     @staticmethod
     def forward(ctx, offsets, reference_points, logits, spatial_shapes):
@@ -42,14 +42,12 @@ class PackSamplingFunction(Function):
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_packed):
+        from . import capi
+
         (spatial_shapes,) = ctx.saved_tensors
         (B, Q, G, L, K, _), dtype, ref_dtype, logit_dtype = ctx.meta
-        g_loc = grad_packed[..., : L * K * 3].reshape(B, Q, G, L, K, 3)
-        extent = spatial_shapes.flip(-1).to(g_loc.dtype)  # (D,H,W) -> (W,H,D) = extents along x,y,z
-        g_off = (g_loc / extent[None, None, None, :, None, :]).to(dtype)
-        g_ref = g_loc.sum(dim=(2, 4)).to(ref_dtype)
-        g_logit = grad_packed[..., L * K * 3:].reshape(B, Q, G, L, K).to(logit_dtype)
-        return g_off, g_ref, g_logit, None
+        g_off, g_ref, g_logit = capi.pack_sampling_backward(grad_packed.float().contiguous(), spatial_shapes, B, Q, G, L, K, dtype)
+        return g_off, g_ref.to(ref_dtype), g_logit.to(logit_dtype), None
 
 
 class MSDeformAttn3D(nn.Module):

@@ -66,7 +66,7 @@ def test_backward_workspace_contract():
     assert lib.fda_backward_scratch_bytes(2, 100, 8, 32, 2, 50, 4, 2) == 2 * 50 * 8 * 2 * 4 * 4
     # image of one batch element (598016 x 256 x 4 B) exceeds L2: counters + one 8-byte entry per (row, point)
     big = lib.fda_backward_scratch_bytes(2, 598016, 8, 32, 3, 1000, 8, 0)
-    assert big == 3 * 2 * 64 * 4 + 2 * 1000 * 8 * 8 * 8
+    assert big == 3 * 2 * 128 * 4 + 2 * 1000 * 8 * 8 * 8
     assert lib.fda_backward_workspace_bytes(2, 598016, 8, 32, 3, 1000, 8, 2, 0) == 2 * 598016 * 256 * 4 + big
     plane = 2 * 1000 * 8 * 3 * 8 * 4
     assert lib.fda_backward_scratch_bytes(2, 598016, 8, 32, 3, 1000, 8, 2) == big + plane

@@ -109,7 +109,7 @@ def test_slab_plan_and_exchange_ranges_tile_the_image():
     shapes = torch.tensor([(32, 64, 256), (16, 32, 128), (8, 16, 64)])
     N, G, D = int(shapes.prod(1).sum()), 8, 32
     plan = capi.bin_plan(shapes, (1, N, G, D), 74752, 8)
-    assert plan == (0, 32, 1)  # level 0 in 32 slabs of one plane: 16.8 MB of image each (target 16 MB)
+    assert plan == (0, 32, 1)  # level 0 in 32 z-slabs of one plane (16.8 MB of image each; the kernels cut each once more along y)
     assert capi.bin_plan(torch.tensor([(4, 8, 8), (2, 4, 4)]), (1, 288, 4, 16), 288, 4) is None  # fits L2: no binning
     for level_first in (True, False):
         sh = shapes if level_first else shapes.flip(0)
