@@ -283,6 +283,37 @@ int fda_pack_sampling_backward(const float *grad_packed, const int64_t *spatial_
                                int num_heads, int num_levels, int num_points, int dtype, void *stream);
 
 /*
+ * DCNv4-3D (volumetric deformable convolution v4), forward and backward:
+ *   output[b, q, g, :] = sum_k m_k * trilinear(value[b], p0(q) + (stencil_k * dilation + offset_k) * offset_scale)[g, :]
+ * value [batch][depth_in][height_in][width_in][group*group_channels]; p_offset [batch][Q][padded_offset_dim] with
+ * Q = depth_out*height_out*width_out and, per group g, K*3 offsets (x, y, z per point) then K mask values at
+ * g*K*4 (K = kernel_d*kernel_h*kernel_w, minus one with remove_center; stencil order w outermost, d innermost);
+ * output / grad_output [batch][Q][group*group_channels]; kernel / stride / pad / dilation are HOST arrays of three
+ * ints in (d, h, w) order; one dtype for all tensors.  softmax != 0 soft-maxes the K masks of a (q, g).
+ *
+ * Replace dcnv4_im2col_cuda / dcnv4_col2im_cuda and the host code around them (reference
+ * csrc/cuda/dcnv4_im2col_cuda.cuh, csrc/cuda/dcnv4_col2im_cuda.cuh, csrc/cuda/dcnv4_cuda.cu:19-189; entry points
+ * csrc/dcnv4.h:7-61).  d_stride / block_thread of the reference are launch hints and have no counterpart here.
+ * The backward zero-fills what it accumulates into and writes both gradients completely (offset-row padding = 0);
+ * gradients come back in the tensors' own dtype.  workspace: fda_dcnv4_backward_workspace_bytes() (an fp32 image of
+ * grad_value for 16-bit dtypes, none for fp32), 16-byte aligned.
+ */
+int fda_dcnv4_output_size(int depth_in, int height_in, int width_in, const int *kernel, const int *stride,
+                          const int *pad, const int *dilation, int *depth_out, int *height_out, int *width_out);
+int fda_dcnv4_forward(const void *value, const void *p_offset, void *output, int batch, int depth_in, int height_in,
+                      int width_in, int group, int group_channels, const int *kernel, const int *stride,
+                      const int *pad, const int *dilation, float offset_scale, int remove_center, int softmax,
+                      int padded_offset_dim, int dtype, int im2col_step, void *stream);
+size_t fda_dcnv4_backward_workspace_bytes(int batch, int depth_in, int height_in, int width_in, int group,
+                                          int group_channels, int dtype);
+int fda_dcnv4_backward(const void *value, const void *p_offset, const void *grad_output, void *grad_value,
+                       void *grad_offset, void *workspace, size_t workspace_bytes, int batch, int depth_in,
+                       int height_in, int width_in, int group, int group_channels, const int *kernel,
+                       const int *stride, const int *pad, const int *dilation, float offset_scale,
+                       int remove_center, int softmax, int padded_offset_dim, int dtype, int im2col_step,
+                       void *stream);
+
+/*
  * Backward pass that needs no workspace from the caller and allocates nothing: same inputs,
  * outputs and results as fda_backward, but the fp32 accumulation image sits in a fixed
  * FDA_NOALLOC_MAX_ELEMENTS-float (64 MiB) array inside the library, present on every GPU that

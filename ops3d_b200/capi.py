@@ -19,7 +19,8 @@ EXPORTS = (
     "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
     "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
-    "fda_pack_sampling", "fda_pack_sampling_backward", "fda_reload_config", "fda_group_reduce_cast",
+    "fda_pack_sampling", "fda_pack_sampling_backward", "fda_dcnv4_forward", "fda_dcnv4_backward",
+    "fda_dcnv4_backward_workspace_bytes", "fda_dcnv4_output_size", "fda_reload_config", "fda_group_reduce_cast",
 )
 BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE = 1, 2, 4, 8
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
@@ -78,6 +79,15 @@ def load() -> ctypes.CDLL:
     lib.fda_pack_sampling.restype = i
     lib.fda_pack_sampling_backward.argtypes = [vp] * 5 + [i] * 6 + [vp]
     lib.fda_pack_sampling_backward.restype = i
+    f = ctypes.c_float
+    lib.fda_dcnv4_output_size.argtypes = [i, i, i] + [vp] * 7
+    lib.fda_dcnv4_output_size.restype = i
+    lib.fda_dcnv4_forward.argtypes = [vp] * 3 + [i] * 6 + [vp] * 4 + [f] + [i] * 5 + [vp]
+    lib.fda_dcnv4_forward.restype = i
+    lib.fda_dcnv4_backward_workspace_bytes.argtypes = [i] * 7
+    lib.fda_dcnv4_backward_workspace_bytes.restype = sz
+    lib.fda_dcnv4_backward.argtypes = [vp] * 6 + [sz] + [i] * 6 + [vp] * 4 + [f] + [i] * 5 + [vp]
+    lib.fda_dcnv4_backward.restype = i
     lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
     lib.fda_cast_grad_value.restype = i
     lib.fda_backward_noalloc.argtypes = [vp] * 7 + [i] * 10 + [vp]
@@ -334,3 +344,49 @@ def pack_sampling_backward(grad_packed, shapes, B, Q, G, L, K, dtype):
                                                 g_logit.data_ptr(), B, Q, G, L, K, DTYPE_CODE[dtype], _stream(grad_packed)))
     _count(1)
     return g_off, g_ref, g_logit
+
+
+def _triple(v):
+    arr = (ctypes.c_int * 3)(*[int(x) for x in v])
+    return arr
+
+
+def dcnv4_output_size(size_in, kernel, stride, pad, dilation):
+    """``(depth_out, height_out, width_out)`` of a DCNv4-3D layer (all triples in (d, h, w) order)."""
+    out = [ctypes.c_int(0) for _ in range(3)]
+    check(load().fda_dcnv4_output_size(*[int(x) for x in size_in], _triple(kernel), _triple(stride), _triple(pad),
+                                       _triple(dilation), *[ctypes.addressof(o) for o in out]))
+    return tuple(o.value for o in out)
+
+
+def dcnv4_forward(value, p_offset, kernel, stride, pad, dilation, group, group_channels, offset_scale, remove_center,
+                  softmax, im2col_step=64):
+    """``fda_dcnv4_forward``: value ``[B, Din, Hin, Win, G*Dg]``, p_offset ``[B, Do, Ho, Wo, padded]`` ->
+    ``[B, Do, Ho, Wo, G*Dg]``."""
+    B, Din, Hin, Win, C = value.shape
+    Do, Ho, Wo = dcnv4_output_size((Din, Hin, Win), kernel, stride, pad, dilation)
+    out = torch.empty(B, Do, Ho, Wo, C, dtype=value.dtype, device=value.device)
+    with torch.cuda.device(value.device):
+        check(load().fda_dcnv4_forward(value.data_ptr(), p_offset.data_ptr(), out.data_ptr(), B, Din, Hin, Win, group,
+                                       group_channels, _triple(kernel), _triple(stride), _triple(pad), _triple(dilation),
+                                       float(offset_scale), int(remove_center), int(bool(softmax)), p_offset.shape[-1],
+                                       DTYPE_CODE[value.dtype], im2col_step, _stream(value)))
+    _count(1)
+    return out
+
+
+def dcnv4_backward(value, p_offset, grad_output, kernel, stride, pad, dilation, group, group_channels, offset_scale,
+                   remove_center, softmax, im2col_step=64):
+    """``fda_dcnv4_backward`` -> ``(grad_value, grad_offset)`` in the inputs' dtype."""
+    B, Din, Hin, Win, C = value.shape
+    grad_value, grad_offset = torch.empty_like(value), torch.empty_like(p_offset)
+    need = int(load().fda_dcnv4_backward_workspace_bytes(B, Din, Hin, Win, group, group_channels, DTYPE_CODE[value.dtype]))
+    ws = torch.empty((need + 3) // 4, dtype=torch.float32, device=value.device) if need else None
+    with torch.cuda.device(value.device):
+        check(load().fda_dcnv4_backward(value.data_ptr(), p_offset.data_ptr(), grad_output.data_ptr(), grad_value.data_ptr(),
+                                        grad_offset.data_ptr(), ws.data_ptr() if ws is not None else None, need, B, Din, Hin,
+                                        Win, group, group_channels, _triple(kernel), _triple(stride), _triple(pad),
+                                        _triple(dilation), float(offset_scale), int(remove_center), int(bool(softmax)),
+                                        p_offset.shape[-1], DTYPE_CODE[value.dtype], im2col_step, _stream(value)))
+    _count(1 + (1 if need else 0))
+    return grad_value, grad_offset

@@ -124,10 +124,88 @@ std::vector<at::Tensor> flash_deform_attn_backward(const at::Tensor &value, cons
     return {grad_value, grad_packed};
 }
 
+// DCNv4-3D with the positional signatures of the reference's binding (csrc/dcnv4.h:7-61, registered at
+// csrc/vision.cpp:20-21).  d_stride and block_thread are the reference's launch hints: accepted, ignored.
+struct DcnDims {
+    int B, Din, Hin, Win, C, padded;
+};
+
+DcnDims check_dcn(const at::Tensor &value, const at::Tensor &p_offset, int group, int group_channels) {
+    check_cuda_contiguous(value, "input");
+    check_cuda_contiguous(p_offset, "offset");
+    TORCH_CHECK(value.dim() == 5, "value must be [B, D, H, W, C]");
+    TORCH_CHECK(p_offset.dim() == 5, "p_offset must be [B, D_out, H_out, W_out, padded_offset_dim]");
+    TORCH_CHECK(p_offset.scalar_type() == value.scalar_type(), "p_offset must have the dtype of value");
+    TORCH_CHECK(value.device() == p_offset.device(), "all tensors must be on the same device");
+    DcnDims d;
+    d.B = (int)value.size(0); d.Din = (int)value.size(1); d.Hin = (int)value.size(2); d.Win = (int)value.size(3);
+    d.C = (int)value.size(4); d.padded = (int)p_offset.size(4);
+    TORCH_CHECK(d.C == group * group_channels, "Input channels and group times group channels dont match: (", d.C, " vs ",
+                group * group_channels, ").");
+    return d;
+}
+
+at::Tensor dcnv4_forward(const at::Tensor &value, const at::Tensor &p_offset, const int kernel_d, const int kernel_h,
+                         const int kernel_w, const int stride_d, const int stride_h, const int stride_w, const int pad_d,
+                         const int pad_h, const int pad_w, const int dilation_d, const int dilation_h, const int dilation_w,
+                         const int group, const int group_channels, const float offset_scale, const int im2col_step,
+                         const int remove_center, const int d_stride, const int block_thread, const bool softmax) {
+    (void)d_stride; (void)block_thread;
+    const DcnDims d = check_dcn(value, p_offset, group, group_channels);
+    const int kernel[3] = {kernel_d, kernel_h, kernel_w}, stride[3] = {stride_d, stride_h, stride_w};
+    const int pad[3] = {pad_d, pad_h, pad_w}, dilation[3] = {dilation_d, dilation_h, dilation_w};
+    int Do = 0, Ho = 0, Wo = 0;
+    raise_status(fda_dcnv4_output_size(d.Din, d.Hin, d.Win, kernel, stride, pad, dilation, &Do, &Ho, &Wo), "dcnv4_forward");
+    TORCH_CHECK(p_offset.size(0) == d.B && p_offset.size(1) == Do && p_offset.size(2) == Ho && p_offset.size(3) == Wo,
+                "p_offset spatial shape does not match the output volume");
+    c10::cuda::CUDAGuard guard(value.device());
+    at::Tensor output = at::empty({d.B, Do, Ho, Wo, d.C}, value.options());
+    raise_status(fda_dcnv4_forward(value.data_ptr(), p_offset.data_ptr(), output.data_ptr(), d.B, d.Din, d.Hin, d.Win, group,
+                                   group_channels, kernel, stride, pad, dilation, offset_scale, remove_center, softmax ? 1 : 0,
+                                   d.padded, dtype_code(value, "value"), im2col_step,
+                                   at::cuda::getCurrentCUDAStream().stream()),
+                 "dcnv4_forward");
+    return output;
+}
+
+std::vector<at::Tensor> dcnv4_backward(const at::Tensor &value, const at::Tensor &p_offset, const int kernel_d,
+                                       const int kernel_h, const int kernel_w, const int stride_d, const int stride_h,
+                                       const int stride_w, const int pad_d, const int pad_h, const int pad_w,
+                                       const int dilation_d, const int dilation_h, const int dilation_w, const int group,
+                                       const int group_channels, const float offset_scale, const int im2col_step,
+                                       const at::Tensor &grad_output, const int remove_center, const int d_stride,
+                                       const int block_thread, const bool softmax) {
+    (void)d_stride; (void)block_thread;
+    const DcnDims d = check_dcn(value, p_offset, group, group_channels);
+    check_cuda_contiguous(grad_output, "grad_output");
+    TORCH_CHECK(grad_output.scalar_type() == value.scalar_type(), "grad_output must have the dtype of value");
+    const int kernel[3] = {kernel_d, kernel_h, kernel_w}, stride[3] = {stride_d, stride_h, stride_w};
+    const int pad[3] = {pad_d, pad_h, pad_w}, dilation[3] = {dilation_d, dilation_h, dilation_w};
+    const int vdt = dtype_code(value, "value");
+    c10::cuda::CUDAGuard guard(value.device());
+    at::Tensor grad_value = at::empty_like(value);
+    at::Tensor grad_offset = at::empty_like(p_offset);
+    const size_t ws_bytes = fda_dcnv4_backward_workspace_bytes(d.B, d.Din, d.Hin, d.Win, group, group_channels, vdt);
+    at::Tensor workspace;
+    void *ws_ptr = nullptr;
+    if (ws_bytes > 0) {
+        workspace = at::empty({(int64_t)((ws_bytes + 3) / sizeof(float))}, value.options().dtype(at::kFloat));
+        ws_ptr = workspace.data_ptr();
+    }
+    raise_status(fda_dcnv4_backward(value.data_ptr(), p_offset.data_ptr(), grad_output.data_ptr(), grad_value.data_ptr(),
+                                    grad_offset.data_ptr(), ws_ptr, ws_bytes, d.B, d.Din, d.Hin, d.Win, group, group_channels,
+                                    kernel, stride, pad, dilation, offset_scale, remove_center, softmax ? 1 : 0, d.padded, vdt,
+                                    im2col_step, at::cuda::getCurrentCUDAStream().stream()),
+                 "dcnv4_backward");
+    return {grad_value, grad_offset};
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "B200 Flash Deformable 3D Attention (torch binding over the fda_b200 C ABI)";
     m.def("flash_deform_attn_forward", &flash_deform_attn_forward, "Flash Deformable 3D Attention forward (sm_100a)");
     m.def("flash_deform_attn_backward", &flash_deform_attn_backward, "Flash Deformable 3D Attention backward (sm_100a)");
+    m.def("dcnv4_forward", &dcnv4_forward, "DCNv4-3D forward (sm_100a)");
+    m.def("dcnv4_backward", &dcnv4_backward, "DCNv4-3D backward (sm_100a)");
 }

@@ -113,16 +113,16 @@ struct RowGrad {
 // each as 8 x 16 contiguous bytes, so that one reduction request to L2 covers a whole 128-byte line
 // instead of two half-line requests.  acc_even / acc_odd are the two rows' image bases (head offset
 // included, lane offset excluded); weight and offset of the partner row's corner come by shuffle.
+// Core: geometry given (corner offsets, validity, weights).  gx/gy/gz_out are the derivatives of the sample
+// dotted with grad_out w.r.t. the VOXEL coordinates (not yet multiplied by a or by d voxel / d input).
 template <typename VT, bool kPair>
-__device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, float x, float y, float z, float a,
-                                               const VT *lvl, float *acc_lvl, const RowGrad<VT> &go, int red_stride,
-                                               bool active, int gs, uint64_t pol_v, uint64_t pol_g,
-                                               float &gx_out, float &gy_out, float &gz_out, float &da_out,
-                                               float *acc_even = nullptr, float *acc_odd = nullptr) {
+__device__ __forceinline__ void point_backward_geom(const PointGeom &pg, float a,
+                                                    const VT *lvl, float *acc_lvl, const RowGrad<VT> &go, int red_stride,
+                                                    bool active, int gs, uint64_t pol_v, uint64_t pol_g,
+                                                    float &gx_out, float &gy_out, float &gz_out, float &da_out,
+                                                    float *acc_even = nullptr, float *acc_odd = nullptr) {
     constexpr int CPL = Vec16<VT>::kCPL;
     constexpr int NRED = CPL / 4;
-    PointGeom pg;
-    point_geometry(lv, GD, x, y, z, pg);
     uint4 raw[8];
     bool in[8];
 #pragma unroll
@@ -190,10 +190,27 @@ __device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, floa
         gz += __shfl_xor_sync(0xffffffffu, gz, mask);
         da += __shfl_xor_sync(0xffffffffu, da, mask);
     }
+    gx_out = gx;
+    gy_out = gy;
+    gz_out = gz;
+    da_out = da;
+}
+
+// Deformable-attention form: normalised coordinates, gradients w.r.t. them (voxel = coordinate * extent - 0.5).
+template <typename VT, bool kPair>
+__device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, float x, float y, float z, float a,
+                                               const VT *lvl, float *acc_lvl, const RowGrad<VT> &go, int red_stride,
+                                               bool active, int gs, uint64_t pol_v, uint64_t pol_g,
+                                               float &gx_out, float &gy_out, float &gz_out, float &da_out,
+                                               float *acc_even = nullptr, float *acc_odd = nullptr) {
+    PointGeom pg;
+    point_geometry(lv, GD, x, y, z, pg);
+    float gx, gy, gz;
+    point_backward_geom<VT, kPair>(pg, a, lvl, acc_lvl, go, red_stride, active, gs, pol_v, pol_g, gx, gy, gz, da_out,
+                                   acc_even, acc_odd);
     gx_out = a * (float)lv.W * gx;
     gy_out = a * (float)lv.H * gy;
     gz_out = a * (float)lv.D * gz;
-    da_out = da;
 }
 
 template <typename VT, typename PT, bool kPair>
@@ -223,6 +240,7 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
     const bool row_ok = row < p.rows_per_b;
     const bool active = row_ok && lane_c < p.lpg;
     const int LK = p.LK;
+    const float inv_lk = 1.0f / (float)LK;
 
     // Tile row layout (fp32): [0,3LK) coordinates -> coordinate gradients,
     // [3LK,4LK) logits -> dalpha -> logit gradients, [4LK,5LK) exp(logit - max).
@@ -258,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
         const float *prev_da = p.dalpha ? p.dalpha + ((size_t)b * p.rows_per_b + first) * (size_t)LK : nullptr;
         const int nvec = nrows * LK;
         for (int v = lane; v < nvec; v += 32) {
-            const int r = v / LK;
+            const int r = row_of_vector(v, inv_lk);
             const int c = (v - r * LK) * 4;
             const int j = c < 3 * LK ? c / 12 : (c - 3 * LK) >> 2;
             if (!((level_mask >> (j >> p.k_shift)) & 1)) {
@@ -338,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, FDA_BWD_MIN_BLOCKS) fda_backward_ker
     const int nvec = nrows * LK;
     float *next_da = (!p.finalize && p.dalpha) ? p.dalpha + ((size_t)b * p.rows_per_b + first) * (size_t)LK : nullptr;
     for (int v = lane; v < nvec; v += 32) {
-        const int r = v / LK;
+        const int r = row_of_vector(v, inv_lk);
         const int c = (v - r * LK) * 4;
         const float4 f = *reinterpret_cast<const float4 *>(wtile + r * p.row_stride + c);
         store4_stream<PT>(dst + (size_t)v * 4, f);

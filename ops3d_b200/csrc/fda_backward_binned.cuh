@@ -53,19 +53,6 @@ __device__ __forceinline__ LevelGeom level_geom_of(const Problem &p, int l) {
     return lv;
 }
 
-template <typename PT> __device__ __forceinline__ float load1(const PT *p);
-template <> __device__ __forceinline__ float load1<float>(const float *p) { return __ldg(p); }
-template <> __device__ __forceinline__ float load1<__nv_bfloat16>(const __nv_bfloat16 *p) {
-    return __uint_as_float((uint32_t)__ldg(reinterpret_cast<const unsigned short *>(p)) << 16);
-}
-template <> __device__ __forceinline__ float load1<__half>(const __half *p) {
-    return __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(p))));
-}
-template <typename PT> __device__ __forceinline__ void store1(PT *p, float v);
-template <> __device__ __forceinline__ void store1<float>(float *p, float v) { *p = v; }
-template <> __device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
-template <> __device__ __forceinline__ void store1<__half>(__half *p, float v) { *p = __float2half_rn(v); }
-
 template <typename PT>
 __global__ void __launch_bounds__(256) fda_bin_count_kernel(const Problem p) {
     __shared__ BinPlan plan;

@@ -259,6 +259,20 @@ template <> __device__ __forceinline__ void store4_stream<__half>(__half *p, con
     __stcs(reinterpret_cast<uint2 *>(p), make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b)));
 }
 
+// One element <-> fp32.
+template <typename PT> __device__ __forceinline__ float load1(const PT *p);
+template <> __device__ __forceinline__ float load1<float>(const float *p) { return __ldg(p); }
+template <> __device__ __forceinline__ float load1<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    return __uint_as_float((uint32_t)__ldg(reinterpret_cast<const unsigned short *>(p)) << 16);
+}
+template <> __device__ __forceinline__ float load1<__half>(const __half *p) {
+    return __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(p))));
+}
+template <typename PT> __device__ __forceinline__ void store1(PT *p, float v);
+template <> __device__ __forceinline__ void store1<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void store1<__half>(__half *p, float v) { *p = __float2half_rn(v); }
+
 // L2 eviction-priority policies.  The gather re-reads small pyramid levels hundreds of times while
 // the largest level and the per-query rows stream through once; marking the former "evict last"
 // and the latter "evict first" keeps the re-used levels resident in the 126 MB L2.
@@ -371,10 +385,8 @@ struct PointGeom {
     uint32_t off[8];             // element offset of corner (dz,dy,dx) -> index dz*4+dy*2+dx, modulo 2^32
 };
 
-__device__ __forceinline__ void point_geometry(const LevelGeom &lv, int GD, float x, float y, float z, PointGeom &pg) {
-    const float xi = unnormalize(x, (float)lv.W);
-    const float yi = unnormalize(y, (float)lv.H);
-    const float zi = unnormalize(z, (float)lv.D);
+// From voxel coordinates (xi, yi, zi) of the level (cell centres at integers).
+__device__ __forceinline__ void point_geometry_voxel(const LevelGeom &lv, int GD, float xi, float yi, float zi, PointGeom &pg) {
     const float xf = floorf(xi), yf = floorf(yi), zf = floorf(zi);
     pg.wx[0] = __fsub_rn(__fadd_rn(xf, 1.0f), xi); pg.wx[1] = __fsub_rn(xi, xf);
     pg.wy[0] = __fsub_rn(__fadd_rn(yf, 1.0f), yi); pg.wy[1] = __fsub_rn(yi, yf);
@@ -393,13 +405,23 @@ __device__ __forceinline__ void point_geometry(const LevelGeom &lv, int GD, floa
         pg.off[n] = base + ((n & 4) ? sz : 0u) + ((n & 2) ? sy : 0u) + ((n & 1) ? sx : 0u);
 }
 
+// v / LK for the small vector indices of a warp's tile (v < 32 rows * 40 vectors) without an integer division:
+// (v + 0.5) / LK lies at least 0.5 / LK away from the next integer, far more than the rounding error of the product.
+__device__ __forceinline__ int row_of_vector(int v, float inv_lk) { return (int)(((float)v + 0.5f) * inv_lk); }
+
+// From normalised coordinates in [0, 1] (the deformable-attention convention).
+__device__ __forceinline__ void point_geometry(const LevelGeom &lv, int GD, float x, float y, float z, PointGeom &pg) {
+    point_geometry_voxel(lv, GD, unnormalize(x, (float)lv.W), unnormalize(y, (float)lv.H), unnormalize(z, (float)lv.D), pg);
+}
+
 // Stage `nrows` consecutive packed rows (4*LK elements each, contiguous in global memory) into a
 // warp-private shared-memory tile as fp32, `row_stride` floats apart.  Whole warp participates.
 template <typename PT>
 __device__ __forceinline__ void stage_rows(const PT *__restrict__ src, float *tile, int nrows, int LK, int row_stride, int lane) {
     const int nvec = nrows * LK;  // 4-element vectors
+    const float inv_lk = 1.0f / (float)LK;
     for (int v = lane; v < nvec; v += 32) {
-        const int r = v / LK;
+        const int r = row_of_vector(v, inv_lk);
         const int c = (v - r * LK) * 4;
         const float4 f = load4_stream<PT>(src + (size_t)v * 4);
         *reinterpret_cast<float4 *>(tile + r * row_stride + c) = f;

@@ -62,3 +62,29 @@ def test_known_answers():
     want = value[:, (1 * 4 + 2) * 5 + 3].reshape(B, 1, G * D).expand(B, Q, G * D)
     assert torch.allclose(fda_oracle.fused_forward(value, shapes, packed_c, K), want, atol=1e-5)
     assert torch.allclose(c_oracle.forward(value, shapes, lsi, packed_c, K), want, atol=1e-5)
+
+
+def test_dcnv4_oracle_known_answers():
+    """The DCNv4-3D oracle on cases with a closed-form answer: a 3x3x3 stencil whose mask selects the centre point
+    reproduces the input; an extra offset of one voxel along x shifts it (zero beyond the edge); soft-maxed equal
+    masks over a constant volume give the constant away from the border."""
+    from oracle import dcnv4_oracle as o
+
+    B, size, G, Dg = 1, (4, 5, 6), 2, 8
+    k, s, p, d = (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)
+    v, rows, _ = o.make_inputs(B, size, G, Dg, k, s, p, d, 0, seed=1)
+    pts = o.stencil_points(k, 0)
+    K, c = len(pts), pts.index((1, 1, 1))
+    assert K == 27 and rows.shape[-1] == 216 and o.output_size(size, k, s, p, d) == size
+    rows.zero_()
+    body = rows[..., : G * K * 4].reshape(B, *size, G, K * 4)
+    body[..., 3 * K + c] = 1.0
+    out = o.dcnv4_forward(v, rows, k, s, p, d, G, Dg, 1.0, 0, False)
+    assert (out - v).abs().max().item() < 1e-6
+    body[..., 3 * c] = 1.0
+    out = o.dcnv4_forward(v, rows, k, s, p, d, G, Dg, 1.0, 0, False)
+    assert (out[:, :, :, :-1] - v[:, :, :, 1:]).abs().max().item() < 1e-6 and out[:, :, :, -1].abs().max().item() == 0
+    rows.zero_()
+    out = o.dcnv4_forward(torch.full_like(v, 2.0), rows, k, s, p, d, G, Dg, 1.0, 1, True)
+    assert len(o.stencil_points(k, 1)) == 26
+    assert (out[:, 1:-1, 1:-1, 1:-1] - 2.0).abs().max().item() < 1e-6
