@@ -218,11 +218,13 @@ __global__ void __launch_bounds__(fda::kThreads, 2) dcnv4_backward_kernel(const 
         }
     }
     __syncwarp();
-    if (p.softmax && row_ok) {
+    if (p.softmax) {  // uniform branch: the warp barrier inside is reached by every lane
         float S = 0.f;  // sum_j m_j * dmask_j
-        for (int k = 0; k < K; ++k) S = fmaf(trow[4 * K + k], trow[3 * K + k], S);
+        if (row_ok)
+            for (int k = 0; k < K; ++k) S = fmaf(trow[4 * K + k], trow[3 * K + k], S);
         __syncwarp();
-        for (int k = lane_c; k < K; k += gs) trow[3 * K + k] = trow[4 * K + k] * (trow[3 * K + k] - S);
+        if (row_ok)
+            for (int k = lane_c; k < K; k += gs) trow[3 * K + k] = trow[4 * K + k] * (trow[3 * K + k] - S);
     }
     __syncwarp();
     // write the finished gradient rows (the padding of the offset rows is cleared by the host's memset)

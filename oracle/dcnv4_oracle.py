@@ -40,28 +40,39 @@ def stencil_points(kernel, remove_center):
     return pts
 
 
-def dcnv4_forward(value, p_offset, kernel, stride, pad, dilation, group, group_channels, offset_scale, remove_center, softmax):
-    """value ``[B, Din, Hin, Win, G*Dg]``, p_offset ``[B, Do, Ho, Wo, padded]`` -> ``[B, Do, Ho, Wo, G*Dg]``.
-    Triples are in (d, h, w) order.  Differentiable w.r.t. ``value`` and ``p_offset``."""
-    B, Din, Hin, Win, C = value.shape
-    G, Dg = group, group_channels
-    Do, Ho, Wo = output_size((Din, Hin, Win), kernel, stride, pad, dilation)
+def sampling_positions(p_offset, size_in, kernel, stride, pad, dilation, group, offset_scale, remove_center):
+    """Voxel coordinates ``[B, Q, G, K, 3]`` (w, h, d) of every sampling point, and the raw masks ``[B, Q, G, K]``."""
+    B = p_offset.shape[0]
+    G = group
+    Do, Ho, Wo = output_size(size_in, kernel, stride, pad, dilation)
     pts = stencil_points(kernel, remove_center)
     K = len(pts)
     Q = Do * Ho * Wo
     rows = p_offset.reshape(B, Q, -1)[..., : G * K * 4].reshape(B, Q, G, K * 4)
     off = rows[..., : K * 3].reshape(B, Q, G, K, 3)          # (x, y, z) = (w, h, d)
     mask = rows[..., K * 3:]                                   # [B, Q, G, K]
-    if softmax:
-        mask = F.softmax(mask, dim=-1)
-    dev, dt = value.device, value.dtype
+    dev, dt = p_offset.device, p_offset.dtype
     zz, yy, xx = torch.meshgrid(torch.arange(Do, device=dev), torch.arange(Ho, device=dev), torch.arange(Wo, device=dev), indexing="ij")
     (kd, kh, kw), (sd, sh, sw), (pd, ph, pw), (dd, dh, dw) = kernel, stride, pad, dilation
     half = ((dw * (kw - 1)) >> 1, (dh * (kh - 1)) >> 1, (dd * (kd - 1)) >> 1)
     p0 = torch.stack([half[0] - pw + xx * sw, half[1] - ph + yy * sh, half[2] - pd + zz * sd], -1).reshape(1, Q, 1, 1, 3).to(dt)
     p0 = p0 - torch.tensor(half, device=dev, dtype=dt) * offset_scale
     st = torch.tensor([(i * dw, j * dh, k * dd) for i, j, k in pts], device=dev, dtype=dt).reshape(1, 1, 1, K, 3)
-    pos = p0 + (st + off) * offset_scale                       # voxel coordinates (w, h, d)
+    return p0 + (st + off) * offset_scale, mask
+
+
+def dcnv4_forward(value, p_offset, kernel, stride, pad, dilation, group, group_channels, offset_scale, remove_center, softmax):
+    """value ``[B, Din, Hin, Win, G*Dg]``, p_offset ``[B, Do, Ho, Wo, padded]`` -> ``[B, Do, Ho, Wo, G*Dg]``.
+    Triples are in (d, h, w) order.  Differentiable w.r.t. ``value`` and ``p_offset``."""
+    B, Din, Hin, Win, C = value.shape
+    G, Dg = group, group_channels
+    Do, Ho, Wo = output_size((Din, Hin, Win), kernel, stride, pad, dilation)
+    Q = Do * Ho * Wo
+    pos, mask = sampling_positions(p_offset, (Din, Hin, Win), kernel, stride, pad, dilation, G, offset_scale, remove_center)
+    K = pos.shape[3]
+    if softmax:
+        mask = F.softmax(mask, dim=-1)
+    dev, dt = value.device, value.dtype
     size = torch.tensor([Win, Hin, Din], device=dev, dtype=dt)
     grid = 2 * (pos + 0.5) / size - 1                          # grid_sample un-normalises this back to pos
     vol = value.reshape(B, Din, Hin, Win, G, Dg).permute(0, 4, 5, 1, 2, 3).reshape(B * G, Dg, Din, Hin, Win)
@@ -94,3 +105,24 @@ def make_inputs(B, size_in, G, Dg, kernel, stride, pad, dilation, remove_center,
     body[..., : K * 3] *= offset_std
     grad_out = torch.randn(B, Do, Ho, Wo, G * Dg, generator=torch.Generator().manual_seed(seed + 1))
     return value, rows, grad_out
+
+
+def keep_positions_off_the_grid(p_offset, size_in, kernel, stride, pad, dilation, group, offset_scale, remove_center, margin=2e-3):
+    """Returns ``p_offset`` (same dtype) with the offsets nudged wherever a sampling position would land within
+    ``margin`` of an integer voxel coordinate.  Trilinear interpolation has a left and a right derivative there; with
+    16-bit offsets exact hits are common (offset == stencil centre - stencil index), and which side an implementation
+    takes is not part of the operator's contract."""
+    out = p_offset.clone()
+    dt = out.dtype
+    G = group
+    K = kernel[0] * kernel[1] * kernel[2] - (1 if remove_center else 0)
+    B = out.shape[0]
+    for _ in range(4):
+        pos, _ = sampling_positions(out.float(), size_in, kernel, stride, pad, dilation, G, offset_scale, remove_center)
+        near = (pos - pos.round()).abs() < margin
+        if not bool(near.any()):
+            break
+        body = out.reshape(B, -1, out.shape[-1])[..., : G * K * 4].reshape(B, -1, G, K * 4)
+        off = body[..., : K * 3].reshape(B, -1, G, K, 3)
+        off += (near.to(dt) * 0.171).to(dt)   # views into `out`
+    return out
