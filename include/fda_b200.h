@@ -314,6 +314,37 @@ int fda_dcnv4_backward(const void *value, const void *p_offset, const void *grad
                        void *stream);
 
 /*
+ * ROI-Align 3D.  features [N][C][D][H][W] (channels first, as the reference's op), rois [num_rois][7] =
+ * (batch index, x1, y1, z1, x2, y2, z2) in input coordinates (scaled by spatial_scale), output
+ * [num_rois][C][pooled_depth][pooled_height][pooled_width]; sampling_ratio <= 0 = adaptive (ceil(roi extent / bins)
+ * samples per bin and axis); order 0 = nearest, 1 = trilinear.  Forward: features, rois and output share `dtype`,
+ * accumulation in fp32.  Backward: grad_output of grad_output_dtype, rois and grad_features fp32; grad_features must
+ * be zero-filled by the caller (the reference's contract) and is accumulated into with fp32 atomics.
+ * Replace roi_align_3d_forward / roi_align_3d_backward (reference csrc/roi_align_3d.h,
+ * csrc/cuda/roi_align_3d_cuda_kernel.cuh:31,110, csrc/cuda/interpolation_helpers_3d.h).
+ */
+int fda_roi_align3d_forward(const void *features, const void *rois, void *output, int num_rois, int channels,
+                            int depth, int height, int width, int pooled_depth, int pooled_height,
+                            int pooled_width, float spatial_scale, int sampling_ratio, int order, int dtype,
+                            void *stream);
+int fda_roi_align3d_backward(const void *grad_output, const float *rois, float *grad_features, int num_rois,
+                             int channels, int depth, int height, int width, int pooled_depth,
+                             int pooled_height, int pooled_width, float spatial_scale, int sampling_ratio,
+                             int order, int grad_output_dtype, void *stream);
+
+/*
+ * NMS 3D on boxes ALREADY SORTED by decreasing score: boxes_sorted [num_boxes][6] = (x1, y1, z1, x2, y2, z2) fp32.
+ * A box is dropped when its IoU with an earlier kept box exceeds iou_threshold.  keep [num_boxes] receives the
+ * positions (in the sorted order) of the kept boxes, *num_keep (device int) their number; workspace holds the
+ * pairwise bit matrix (fda_nms3d_workspace_bytes).  Both the matrix and the greedy sweep run on the device.
+ * Replace nms_3d_cuda (reference csrc/cuda/nms_3d_cuda.cu:49-162; entry point csrc/nms_3d.h:28), whose sweep runs
+ * on the host after copying the matrix back.
+ */
+size_t fda_nms3d_workspace_bytes(int num_boxes);
+int fda_nms3d(const float *boxes_sorted, int num_boxes, float iou_threshold, void *workspace,
+              size_t workspace_bytes, long long *keep, int *num_keep, void *stream);
+
+/*
  * Backward pass that needs no workspace from the caller and allocates nothing: same inputs,
  * outputs and results as fda_backward, but the fp32 accumulation image sits in a fixed
  * FDA_NOALLOC_MAX_ELEMENTS-float (64 MiB) array inside the library, present on every GPU that

@@ -20,7 +20,8 @@ EXPORTS = (
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
     "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
     "fda_pack_sampling", "fda_pack_sampling_backward", "fda_dcnv4_forward", "fda_dcnv4_backward",
-    "fda_dcnv4_backward_workspace_bytes", "fda_dcnv4_output_size", "fda_reload_config", "fda_group_reduce_cast",
+    "fda_dcnv4_backward_workspace_bytes", "fda_dcnv4_output_size", "fda_roi_align3d_forward", "fda_roi_align3d_backward",
+    "fda_nms3d", "fda_nms3d_workspace_bytes", "fda_reload_config", "fda_group_reduce_cast",
 )
 BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE = 1, 2, 4, 8
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
@@ -88,6 +89,14 @@ def load() -> ctypes.CDLL:
     lib.fda_dcnv4_backward_workspace_bytes.restype = sz
     lib.fda_dcnv4_backward.argtypes = [vp] * 6 + [sz] + [i] * 6 + [vp] * 4 + [f] + [i] * 5 + [vp]
     lib.fda_dcnv4_backward.restype = i
+    lib.fda_roi_align3d_forward.argtypes = [vp] * 3 + [i] * 8 + [f] + [i] * 3 + [vp]
+    lib.fda_roi_align3d_forward.restype = i
+    lib.fda_roi_align3d_backward.argtypes = [vp] * 3 + [i] * 8 + [f] + [i] * 3 + [vp]
+    lib.fda_roi_align3d_backward.restype = i
+    lib.fda_nms3d_workspace_bytes.argtypes = [i]
+    lib.fda_nms3d_workspace_bytes.restype = sz
+    lib.fda_nms3d.argtypes = [vp, i, f, vp, sz, vp, vp, vp]
+    lib.fda_nms3d.restype = i
     lib.fda_cast_grad_value.argtypes = [vp, vp, sz, i, vp]
     lib.fda_cast_grad_value.restype = i
     lib.fda_backward_noalloc.argtypes = [vp] * 7 + [i] * 10 + [vp]
@@ -390,3 +399,44 @@ def dcnv4_backward(value, p_offset, grad_output, kernel, stride, pad, dilation, 
                                         p_offset.shape[-1], DTYPE_CODE[value.dtype], im2col_step, _stream(value)))
     _count(1 + (1 if need else 0))
     return grad_value, grad_offset
+
+
+def roi_align3d_forward(features, rois, output_size, spatial_scale, sampling_ratio, order):
+    """``fda_roi_align3d_forward``: features ``[N,C,D,H,W]``, rois ``[n,7]`` (same dtype) -> ``[n,C,pd,ph,pw]``."""
+    N, C, D, H, W = features.shape
+    pd, ph, pw = output_size
+    out = torch.empty(rois.shape[0], C, pd, ph, pw, dtype=features.dtype, device=features.device)
+    with torch.cuda.device(features.device):
+        check(load().fda_roi_align3d_forward(features.data_ptr(), rois.data_ptr(), out.data_ptr(), rois.shape[0], C, D, H, W,
+                                             pd, ph, pw, float(spatial_scale), int(sampling_ratio), int(order),
+                                             DTYPE_CODE[features.dtype], _stream(features)))
+    _count(1)
+    return out
+
+
+def roi_align3d_backward(grad_output, rois, feature_shape, spatial_scale, sampling_ratio, order):
+    """``fda_roi_align3d_backward`` -> fp32 ``grad_features`` of ``feature_shape``."""
+    N, C, D, H, W = feature_shape
+    n, _, pd, ph, pw = grad_output.shape
+    grad = torch.zeros(N, C, D, H, W, dtype=torch.float32, device=grad_output.device)
+    with torch.cuda.device(grad_output.device):
+        check(load().fda_roi_align3d_backward(grad_output.data_ptr(), rois.data_ptr(), grad.data_ptr(), n, C, D, H, W, pd, ph, pw,
+                                              float(spatial_scale), int(sampling_ratio), int(order),
+                                              DTYPE_CODE[grad_output.dtype], _stream(grad_output)))
+    _count(1)
+    return grad
+
+
+def nms3d(boxes_sorted, iou_threshold):
+    """``fda_nms3d`` on fp32 boxes ``[n,6]`` already sorted by decreasing score -> positions of the kept boxes."""
+    n = boxes_sorted.shape[0]
+    dev = boxes_sorted.device
+    keep = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
+    num = torch.zeros(1, dtype=torch.int32, device=dev)
+    need = int(load().fda_nms3d_workspace_bytes(n))
+    ws = torch.empty(max(need // 8, 1), dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        check(load().fda_nms3d(boxes_sorted.data_ptr(), n, float(iou_threshold), ws.data_ptr(), need, keep.data_ptr(),
+                               num.data_ptr(), _stream(boxes_sorted)))
+    _count(2 if n else 0)
+    return keep[: int(num.item())]

@@ -200,12 +200,76 @@ std::vector<at::Tensor> dcnv4_backward(const at::Tensor &value, const at::Tensor
     return {grad_value, grad_offset};
 }
 
+// ROI-Align 3D and NMS 3D with the reference's binding signatures (csrc/roi_align_3d.h:96-136, csrc/nms_3d.h:28-44):
+// the forward / backward write into tensors the caller allocated (and, for the backward, zero-filled).
+void roi_align_3d_forward(at::Tensor input, at::Tensor rois, at::Tensor output, int aligned_depth, int aligned_height,
+                          int aligned_width, float spatial_scale, int sampling_ratio, int order) {
+    check_cuda_contiguous(input, "input");
+    check_cuda_contiguous(rois, "rois");
+    check_cuda_contiguous(output, "output");
+    TORCH_CHECK(rois.dim() == 2 && rois.size(1) == 7, "wrong roi size! size_rois should be 7");
+    TORCH_CHECK(input.dim() == 5, "input must be [N, C, D, H, W]");
+    TORCH_CHECK(rois.scalar_type() == input.scalar_type() && output.scalar_type() == input.scalar_type(),
+                "input, rois and output must share one dtype");
+    TORCH_CHECK(output.numel() == rois.size(0) * input.size(1) * (int64_t)aligned_depth * aligned_height * aligned_width,
+                "output must be [num_rois, C, aligned_depth, aligned_height, aligned_width]");
+    c10::cuda::CUDAGuard guard(input.device());
+    raise_status(fda_roi_align3d_forward(input.data_ptr(), rois.data_ptr(), output.data_ptr(), (int)rois.size(0), (int)input.size(1),
+                                         (int)input.size(2), (int)input.size(3), (int)input.size(4), aligned_depth, aligned_height,
+                                         aligned_width, spatial_scale, sampling_ratio, order, dtype_code(input, "input"),
+                                         at::cuda::getCurrentCUDAStream().stream()),
+                 "roi_align_3d_forward");
+}
+
+void roi_align_3d_backward(at::Tensor top_grad, at::Tensor rois, at::Tensor bottom_grad, int aligned_depth, int aligned_height,
+                           int aligned_width, float spatial_scale, int sampling_ratio, int order) {
+    check_cuda_contiguous(top_grad, "top_grad");
+    check_cuda_contiguous(rois, "rois");
+    check_cuda_contiguous(bottom_grad, "bottom_grad");
+    TORCH_CHECK(rois.dim() == 2 && rois.size(1) == 7, "wrong roi size! size_rois should be 7");
+    TORCH_CHECK(bottom_grad.dim() == 5, "bottom_grad must be [N, C, D, H, W]");
+    TORCH_CHECK(rois.scalar_type() == at::kFloat && bottom_grad.scalar_type() == at::kFloat,
+                "rois and bottom_grad must be float32 (gradients accumulate with fp32 atomics)");
+    c10::cuda::CUDAGuard guard(top_grad.device());
+    raise_status(fda_roi_align3d_backward(top_grad.data_ptr(), rois.data_ptr<float>(), bottom_grad.data_ptr<float>(), (int)rois.size(0),
+                                          (int)bottom_grad.size(1), (int)bottom_grad.size(2), (int)bottom_grad.size(3),
+                                          (int)bottom_grad.size(4), aligned_depth, aligned_height, aligned_width, spatial_scale,
+                                          sampling_ratio, order, dtype_code(top_grad, "top_grad"),
+                                          at::cuda::getCurrentCUDAStream().stream()),
+                 "roi_align_3d_backward");
+}
+
+at::Tensor nms_3d(const at::Tensor &dets, const at::Tensor &scores, const float threshold) {
+    TORCH_CHECK(dets.is_cuda() && scores.is_cuda(), "nms_3d: boxes and scores must be CUDA tensors (no CPU implementation)");
+    c10::cuda::CUDAGuard guard(dets.device());
+    if (dets.numel() == 0) return at::empty({0}, dets.options().dtype(at::kLong));
+    TORCH_CHECK(dets.dim() == 2 && dets.size(1) == 6, "boxes must be [N, 6] = (x1, y1, z1, x2, y2, z2)");
+    TORCH_CHECK(scores.numel() == dets.size(0), "one score per box");
+    const int n = (int)dets.size(0);
+    // score order; the stable sort makes ties deterministic (earlier box first)
+    at::Tensor order = std::get<1>(scores.reshape({-1}).sort(/*stable=*/true, /*dim=*/0, /*descending=*/true));
+    at::Tensor sorted = dets.index_select(0, order).to(at::kFloat).contiguous();
+    const size_t ws_bytes = fda_nms3d_workspace_bytes(n);
+    at::Tensor workspace = at::empty({(int64_t)(ws_bytes / 8 + 1)}, dets.options().dtype(at::kLong));
+    at::Tensor keep = at::empty({n}, dets.options().dtype(at::kLong));
+    at::Tensor num = at::zeros({1}, dets.options().dtype(at::kInt));
+    raise_status(fda_nms3d(sorted.data_ptr<float>(), n, threshold, workspace.data_ptr(), ws_bytes,
+                           reinterpret_cast<long long *>(keep.data_ptr<int64_t>()), num.data_ptr<int>(),
+                           at::cuda::getCurrentCUDAStream().stream()),
+                 "nms_3d");
+    const int64_t kept = num.item<int>();  // the one host read: how many boxes survived
+    return order.index_select(0, keep.narrow(0, 0, kept));
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "B200 Flash Deformable 3D Attention (torch binding over the fda_b200 C ABI)";
     m.def("flash_deform_attn_forward", &flash_deform_attn_forward, "Flash Deformable 3D Attention forward (sm_100a)");
     m.def("flash_deform_attn_backward", &flash_deform_attn_backward, "Flash Deformable 3D Attention backward (sm_100a)");
+    m.def("nms_3d", &nms_3d, "non-maximum suppression for 3d boxes (sm_100a)");
+    m.def("roi_align_3d_forward", &roi_align_3d_forward, "ROI-Align 3D forward (sm_100a)");
+    m.def("roi_align_3d_backward", &roi_align_3d_backward, "ROI-Align 3D backward (sm_100a)");
     m.def("dcnv4_forward", &dcnv4_forward, "DCNv4-3D forward (sm_100a)");
     m.def("dcnv4_backward", &dcnv4_backward, "DCNv4-3D backward (sm_100a)");
 }

@@ -3,6 +3,8 @@
     python -m ops3d_b200.microbench cast       fp32 accumulation image -> bf16 grad_value (fda_cast_kernel)
     python -m ops3d_b200.microbench pack       offsets + reference points + logits -> packed rows (fda_pack_kernel)
     python -m ops3d_b200.microbench prepass    slab sorting of the largest level (fda_bin_count / scan / fill kernels)
+    python -m ops3d_b200.microbench project    the layer's query projections + packing: one GEMM that writes the packed
+                                               tensor (project_and_pack) against two GEMMs + fda_pack_kernel
     python -m ops3d_b200.microbench exchange   cross-GPU sum + cast (fda_peer_reduce_cast_kernel); a world of one
                                                on a single GPU, or under torch.distributed.run on several:
         python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
@@ -82,6 +84,37 @@ def bench_prepass(args, dev):
             "rows": B * Q * G, "entries": B * Q * G * K, "ms": ms, "packed_bytes": packed.numel() * 4}
 
 
+def bench_project(args, dev):
+    """Forward of the part of ``MSDeformAttn3D`` that produces ``sampling_loc_attn`` from the queries, both ways."""
+    from .msda3d import PackSamplingFunction, project_and_pack
+
+    B, Q, C, G, L, K = 1, args.queries, 256, 8, 3, 8
+    shapes = torch.tensor(SHAPES5, dtype=torch.long, device=dev)
+    dt = torch.bfloat16
+    query = torch.randn(B, Q, C, device=dev).to(dt)
+    ref = torch.rand(B, Q, L, 3, device=dev)
+    w_off = (torch.randn(G * L * K * 3, C, device=dev) * 0.05).to(dt)
+    b_off = torch.randn(G * L * K * 3, device=dev).to(dt)
+    w_log = (torch.randn(G * L * K, C, device=dev) * 0.05).to(dt)
+    b_log = torch.randn(G * L * K, device=dev).to(dt)
+
+    def fused():
+        return project_and_pack(query, ref, w_off, b_off, w_log, b_log, shapes, G, K)
+
+    def unfused():
+        off = torch.nn.functional.linear(query, w_off, b_off).view(B, Q, G, L, K, 3)
+        log = torch.nn.functional.linear(query, w_log, b_log).view(B, Q, G, L, K)
+        return PackSamplingFunction.apply(off, ref, log, shapes)
+
+    with torch.no_grad():
+        a, b = fused(), unfused()
+        err = (a - b).abs().max().item()   # the unfused path rounds offsets and logits to bf16 before packing
+        ms_f = _time(fused, args.steps, args.warmup)
+        ms_u = _time(unfused, args.steps, args.warmup)
+    return {"what": "query projections + packing, bf16 in, fp32 packed out", "rows": B * Q * G, "packed_bytes": a.numel() * 4,
+            "ms_fused_gemm": ms_f, "ms_two_gemms_plus_pack_kernel": ms_u, "speedup": ms_u / ms_f, "max_abs_difference": err}
+
+
 def bench_exchange(args, dev, rank, world):
     import torch.distributed as dist
 
@@ -118,7 +151,7 @@ def bench_exchange(args, dev, rank, world):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["cast", "pack", "prepass", "exchange"])
+    ap.add_argument("what", choices=["cast", "pack", "prepass", "project", "exchange"])
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--mb", type=float, default=256.0, help="fp32 image size in MB (cast, exchange)")
@@ -139,6 +172,8 @@ def main():
         res = bench_pack(args, dev)
     elif args.what == "prepass":
         res = bench_prepass(args, dev)
+    elif args.what == "project":
+        res = bench_project(args, dev)
     else:
         res = bench_exchange(args, dev, rank, world)
     if rank == 0:

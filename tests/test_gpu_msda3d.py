@@ -22,8 +22,9 @@ def torch_layer(m, query, ref, src, shapes):
     return m.output_proj(ms_deform_attn_core_pytorch_3d(value, shapes, loc, attn))
 
 
+@pytest.mark.parametrize("fused", [True, False], ids=["fused-gemm", "pack-kernel"])
 @pytest.mark.parametrize("K", [4, 8])
-def test_layer_matches_pytorch_composition(K):
+def test_layer_matches_pytorch_composition(K, fused):
     from ops3d_b200.msda3d import MSDeformAttn3D
 
     torch.manual_seed(0)
@@ -44,7 +45,7 @@ def test_layer_matches_pytorch_composition(K):
     want_grads = [query.grad.clone(), src.grad.clone(), ref.grad.clone()] + [p.grad.clone() for p in ref_layer.parameters()]
 
     dev = "cuda"
-    layer = MSDeformAttn3D(C, 2, 4, K).to(dev)
+    layer = MSDeformAttn3D(C, 2, 4, K, fused_projection=fused).to(dev)
     layer.load_state_dict(ref_layer.state_dict())
     q2, s2, r2 = (t.detach().to(dev).requires_grad_(True) for t in (query, src, ref))
     got = layer(q2, r2, s2, shapes.to(dev), lsi.to(dev))
@@ -72,3 +73,32 @@ def test_packing_kernel(dtype):
     want = torch.cat([loc.reshape(B, Q, G, -1), logits.float().reshape(B, Q, G, -1)], -1)
     assert packed.dtype == torch.float32
     assert torch.allclose(packed, want, rtol=1e-6, atol=1e-6)
+
+
+def test_fused_projection_bf16_matches_fp32_composition():
+    """The one-GEMM projection + packing in bf16 against the fp32 composition on the same (bf16-rounded) tensors:
+    coordinates to 2e-2 of a voxel-normalised unit, i.e. within the 16-bit tolerance of the operator's inputs, and
+    the reference points themselves carried exactly (three 16-bit terms)."""
+    from ops3d_b200.msda3d import project_and_pack
+
+    torch.manual_seed(2)
+    dev = "cuda"
+    B, Q, C, G, L, K = 2, 50, 64, 4, 3, 4
+    shapes = torch.tensor([(8, 16, 32), (4, 8, 16), (2, 4, 8)], device=dev)
+    q = torch.randn(B, Q, C, device=dev).bfloat16()
+    ref = torch.rand(B, Q, L, 3, device=dev)
+    wo = (torch.randn(G * L * K * 3, C, device=dev) * 0.1).bfloat16()
+    bo = torch.randn(G * L * K * 3, device=dev).bfloat16()
+    wl = (torch.randn(G * L * K, C, device=dev) * 0.1).bfloat16()
+    bl = torch.randn(G * L * K, device=dev).bfloat16()
+    packed = project_and_pack(q, ref, wo, bo, wl, bl, shapes, G, K)
+    off = (q.float() @ wo.float().t() + bo.float()).view(B, Q, G, L, K, 3)
+    lg = (q.float() @ wl.float().t() + bl.float()).view(B, Q, G, L, K)
+    loc = ref[:, :, None, :, None, :] + off / shapes.flip(-1).float()[None, None, None, :, None, :]
+    want = torch.cat([loc.reshape(B, Q, G, -1), lg.reshape(B, Q, G, -1)], -1)
+    assert packed.dtype == torch.float32 and packed.shape == want.shape
+    assert (packed - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    # zero weights and biases: the packed coordinates are the reference points, to fp32 rounding
+    z = project_and_pack(q, ref, wo * 0, bo * 0, wl * 0, bl * 0, shapes, G, K)
+    want_ref = ref[:, :, None, :, None, :].expand(B, Q, G, L, K, 3).reshape(B, Q, G, -1)
+    assert (z[..., : L * K * 3] - want_ref).abs().max().item() <= 3e-7

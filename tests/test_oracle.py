@@ -88,3 +88,33 @@ def test_dcnv4_oracle_known_answers():
     out = o.dcnv4_forward(torch.full_like(v, 2.0), rows, k, s, p, d, G, Dg, 1.0, 1, True)
     assert len(o.stencil_points(k, 1)) == 26
     assert (out[:, 1:-1, 1:-1, 1:-1] - 2.0).abs().max().item() < 1e-6
+
+
+def test_detection_oracles_known_answers():
+    """NMS oracle on the reference's own known-answer cases (reference tests/test_nms.py:17-50) and ROI-Align oracle on
+    closed-form cases: a constant volume pools to the constant; the backward of ones spreads exactly one unit per output
+    element while every sample lies inside the volume."""
+    import numpy as np
+
+    from oracle import detection_oracle as o
+
+    boxes = np.tile(np.array([0, 0, 0, 100, 100, 100], np.float32), (1000, 1))
+    scores = np.zeros(1000, np.float32)
+    scores[0] = 0.9
+    assert o.nms3d(boxes, scores, 0.1) == [0]
+    two = np.array([[0, 0, 0, 10, 10, 10], [20, 20, 20, 30, 30, 30]], np.float32)
+    assert o.nms3d(two, np.array([0.6, 0.7], np.float32), 0.5) == [1, 0]
+    assert abs(o.iou3d([0, 0, 0, 2, 2, 2], [1, 1, 1, 3, 3, 3]) - 1 / 15) < 1e-6
+    feats = np.full((1, 2, 4, 5, 6), 3.0)
+    rois = np.array([[0, 0.5, 0.5, 0.5, 4.2, 3.7, 2.9]], np.float32)
+    for order in (0, 1):
+        out = o.roi_align3d_forward(feats, rois, (2, 2, 2), 1.0, 2, order)
+        assert np.abs(out - 3.0).max() < 1e-9
+        grad = o.roi_align3d_backward(np.ones((1, 2, 2, 2, 2)), rois, (1, 2, 4, 5, 6), 1.0, 2, order)
+        assert abs(grad.sum() - 16.0) < 1e-9
+    # a roi of one voxel around a cell centre returns that cell (nearest and linear agree at integer positions)
+    vol = np.arange(2 * 3 * 4 * 5, dtype=np.float64).reshape(1, 2, 3, 4, 5)
+    roi = np.array([[0, 1.5, 0.5, 0.5, 2.5, 1.5, 1.5]], np.float32)   # x in [1.5,2.5] -> sample at x = 2, y = 1, z = 1
+    for order in (0, 1):
+        out = o.roi_align3d_forward(vol, roi, (1, 1, 1), 1.0, 1, order)
+        assert np.allclose(out[0, :, 0, 0, 0], vol[0, :, 1, 1, 2])
