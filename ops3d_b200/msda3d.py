@@ -94,11 +94,9 @@ def project_and_pack(query, reference_points, w_offsets, b_offsets, w_logits, b_
     col_extent = extent[:, None, :].expand(L, K, 3).reshape(1, LK * 3, 1)               # per coordinate column of a head
     w_pack = torch.cat([w_offsets.float().view(G, LK * 3, C) / col_extent, w_logits.float().view(G, LK, C)], 1)
     b_pack = torch.cat([b_offsets.float().view(G, LK * 3) / col_extent[..., 0], b_logits.float().view(G, LK)], 1)
-    sel = torch.zeros(L, K, 3, L, 3, device=query.device)                              # coordinate column (l,k,axis) <- ref (l,axis)
-    for l in range(L):
-        for axis in range(3):
-            sel[l, :, axis, l, axis] = 1.0
-    sel = torch.cat([sel.view(LK * 3, L * 3), sel.new_zeros(LK, L * 3)], 0)[None].expand(G, 4 * LK, L * 3)
+    # coordinate column (l, k, axis) takes reference value (l, axis): a one-hot block; logit columns take none
+    sel = torch.eye(L * 3, device=query.device).view(L, 1, 3, L * 3).expand(L, K, 3, L * 3).reshape(LK * 3, L * 3)
+    sel = torch.cat([sel, sel.new_zeros(LK, L * 3)], 0)[None].expand(G, 4 * LK, L * 3)
     extra = 1 + 9 * L
     pad = (-(C + extra)) % 8
     w_aug = torch.cat([w_pack, b_pack[..., None], sel, sel, sel, w_pack.new_zeros(G, 4 * LK, pad)], -1)

@@ -13,9 +13,13 @@ CPU implementation of this operator):
   normalised position ``(2*(p + 0.5)/size - 1)``, which un-normalises back to ``p``;
 * gradients (``csrc/cuda/dcnv4_col2im_cuda.cuh:48-245``): autograd through the same expression.
 
-Parity pin: PARITY UNPINNED against the reference -- it ships no golden vectors, tests or CPU path for
-this operator, and its CUDA kernels are not built in this repository's test flow.  The trilinear core
-is the one the pinned deformable-attention oracle uses (``fda_oracle.py``).
+Parity pin: PINNED to outputs of the reference's own CUDA kernels.  ``tests/golden/dcnv4_*.npz`` were produced by
+``tests/golden/make_golden_dcnv4.py`` on a B200 from the reference sources compiled unmodified
+(``baseline/build_ref_cuda.sh <checkout> --dcnv4``); ``tests/test_oracle.py`` checks this module against them:
+``out`` and ``grad_value`` in all five cases, ``grad_offset`` in four.  The fifth (soft-maxed masks, 16 channels per
+group) goes through the reference's ``backward_kernel_dcn_warp_primitive``, whose soft-max backward block is misplaced
+inside the outermost stencil loop (``csrc/cuda/dcnv4_col2im_cuda.cuh:520-533``) and writes garbage; the soft-max
+backward is pinned instead by two cases with 48 channels per group, which take ``backward_kernel_dcn`` (``:225-237``).
 """
 from __future__ import annotations
 

@@ -43,7 +43,24 @@ def pytest_collection_modifyitems(config, items):
 
 
 def golden_names():
-    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+    """Fixtures of the attention operator (made by the reference's PyTorch implementation)."""
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz"))
+                  if not os.path.basename(p).startswith("dcnv4_"))
+
+
+def dcnv4_golden_names():
+    """Fixtures of DCNv4-3D (made by the reference's CUDA kernels, tests/golden/make_golden_dcnv4.py)."""
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "dcnv4_*.npz")))
+
+
+def load_dcnv4_golden(name):
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    d = {k: torch.from_numpy(z[k]) for k in ("value", "offset", "grad_out", "out", "grad_value", "grad_offset")}
+    d["args"] = (tuple(int(v) for v in z["kernel"]), tuple(int(v) for v in z["stride"]), tuple(int(v) for v in z["pad"]),
+                 tuple(int(v) for v in z["dilation"]), int(z["group"]), int(z["group_channels"]), float(z["offset_scale"]),
+                 int(z["remove_center"]), bool(z["softmax"]))
+    d["grad_offset_usable"] = bool(z["grad_offset_usable"])
+    return d
 
 
 def load_golden(name):

@@ -1,6 +1,6 @@
-"""DCNv4-3D kernels (through the C ABI and through ``ops3d._C`` / ``DCNv4Function``) against the CPU oracle
-(``oracle/dcnv4_oracle.py``: a PyTorch restatement of the reference's CUDA kernels; the reference has no tests or
-golden vectors for this operator).  Tolerances as for the attention operator: fp32 max-abs <= 1e-4 * max(1, |ref|max),
+"""DCNv4-3D kernels (through the C ABI and through ``ops3d._C`` / ``DCNv4Function``) against fixtures produced by the
+reference's own CUDA kernels (``tests/golden/dcnv4_*.npz``) and against the CPU oracle (``oracle/dcnv4_oracle.py``: a
+PyTorch restatement of those kernels, pinned to the same fixtures).  Tolerances as for the attention operator: fp32 max-abs <= 1e-4 * max(1, |ref|max),
 16-bit <= 2e-2 * |ref|max against the fp32 oracle on the same rounded inputs.
 
 Sampling positions are kept off the voxel grid (``oracle.keep_positions_off_the_grid``): with 16-bit offsets many positions
@@ -10,6 +10,7 @@ other one."""
 import pytest
 import torch
 
+from conftest import dcnv4_golden_names, load_dcnv4_golden
 from oracle import dcnv4_oracle as oracle
 from ops3d_b200 import capi
 
@@ -51,6 +52,21 @@ def test_dcnv4_matches_oracle(case, dtype):
     assert (goff.float().cpu() - ref_goff).abs().max().item() <= _tol(dtype, ref_goff)
     K = kernel[0] * kernel[1] * kernel[2] - rc
     assert goff[..., G * K * 4:].abs().max().item() == 0 if goff.shape[-1] > G * K * 4 else True  # padding gets zero gradient
+
+
+@pytest.mark.parametrize("name", dcnv4_golden_names())
+def test_dcnv4_matches_reference_kernel_fixtures(name):
+    g = load_dcnv4_golden(name)
+    kernel, stride, pad, dilation, G, Dg, scale, rc, softmax = g["args"]
+    dev = "cuda"
+    v, o, go = g["value"].to(dev), g["offset"].to(dev), g["grad_out"].to(dev)
+    out = capi.dcnv4_forward(v, o, kernel, stride, pad, dilation, G, Dg, scale, rc, softmax)
+    gv, goff = capi.dcnv4_backward(v, o, go, kernel, stride, pad, dilation, G, Dg, scale, rc, softmax)
+    torch.cuda.synchronize()
+    assert (out.cpu() - g["out"]).abs().max().item() <= 1e-4 * max(1.0, g["out"].abs().max().item())
+    assert (gv.cpu() - g["grad_value"]).abs().max().item() <= 1e-4 * max(1.0, g["grad_value"].abs().max().item())
+    if g["grad_offset_usable"]:  # else: the reference's own result is garbage there (see the fixture generator)
+        assert (goff.cpu() - g["grad_offset"]).abs().max().item() <= 1e-4 * max(1.0, g["grad_offset"].abs().max().item())
 
 
 def test_binding_and_autograd_wrapper():
