@@ -4,6 +4,7 @@
 # this repository's kernels.  Takes about ten minutes (the reference instantiates ~700 kernels).
 #   build_ref_cuda.sh <checkout>            -> baseline/_ref/ops3d_ref_C.so       (deformable attention; timed by bench.py)
 #   build_ref_cuda.sh <checkout> --dcnv4    -> baseline/_ref/ops3d_ref_dcnv4.so   (DCNv4-3D; golden vectors for the oracle)
+#   build_ref_cuda.sh <checkout> --detection -> baseline/_ref/ops3d_ref_detection.so (ROI-Align 3D + NMS 3D; golden vectors)
 set -euo pipefail
 REF="${1:?path of the reference checkout}"
 WHAT="${2:-}"
@@ -29,6 +30,20 @@ if [ "$WHAT" = "--dcnv4" ]; then
       -L"$TORCH_LIB" -Wl,-rpath,"$TORCH_LIB" -L/usr/local/cuda/lib64 -lc10 -lc10_cuda -ltorch_cpu -ltorch_cuda -ltorch -ltorch_python -lcudart
   rm -f "$OUT"/*.o
   echo "built $OUT/ops3d_ref_dcnv4.so"
+  exit 0
+fi
+if [ "$WHAT" = "--detection" ]; then
+  COMMON="-O3 -std=c++17 -DTORCH_EXTENSION_NAME=ops3d_ref_detection -DTORCH_API_INCLUDE_EXTENSION_H -D_GLIBCXX_USE_CXX11_ABI=$ABI $INC"
+  for tu in roi_align_3d_cuda nms_3d_cuda; do
+    nvcc -gencode arch=compute_100a,code=sm_100a $COMMON -DWITH_CUDA -DCUDA_HAS_FP16=1 \
+         -D__CUDA_NO_HALF_OPERATORS__ -D__CUDA_NO_HALF_CONVERSIONS__ -D__CUDA_NO_HALF2_OPERATORS__ \
+         -Xcompiler -fPIC -w -c "$REF/csrc/cuda/$tu.cu" -o "$OUT/$tu.o"
+  done
+  g++ $COMMON -fPIC -w -I"$REF/csrc" -c "$HERE/ref_detection_binding.cpp" -o "$OUT/ref_detection_binding.o"
+  g++ -shared "$OUT/roi_align_3d_cuda.o" "$OUT/nms_3d_cuda.o" "$OUT/ref_detection_binding.o" -o "$OUT/ops3d_ref_detection.so" \
+      -L"$TORCH_LIB" -Wl,-rpath,"$TORCH_LIB" -L/usr/local/cuda/lib64 -lc10 -lc10_cuda -ltorch_cpu -ltorch_cuda -ltorch -ltorch_python -lcudart
+  rm -f "$OUT"/*.o
+  echo "built $OUT/ops3d_ref_detection.so"
   exit 0
 fi
 COMMON="-O3 -std=c++17 -DTORCH_EXTENSION_NAME=ops3d_ref_C -DTORCH_API_INCLUDE_EXTENSION_H -D_GLIBCXX_USE_CXX11_ABI=$ABI $INC"

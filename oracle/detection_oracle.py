@@ -9,8 +9,10 @@ Plain-Python / numpy restatements of the reference's CUDA kernels (the reference
 * ``nms3d``: IoU of ``csrc/cuda/nms_3d_cuda.cu:16-27`` and the greedy sweep of ``:133-157`` (score order, a box is
   dropped when its IoU with an earlier kept box exceeds the threshold).
 
-Parity pin: the NMS oracle is pinned by the reference's own known-answer tests (``tests/test_nms.py:17-50``, restated
-in ``tests/test_oracle.py``); ROI-Align is PARITY UNPINNED (the reference has no test or golden vector for it).
+Parity pin: PINNED to outputs of the reference's own CUDA kernels.  ``tests/golden/roi_align3d_*.npz`` and
+``tests/golden/nms3d_*.npz`` were produced by ``tests/golden/make_golden_detection.py`` on a B200 from the reference
+sources compiled unmodified (``baseline/build_ref_cuda.sh <checkout> --detection``); ``tests/test_oracle.py`` checks this
+module against them, and restates the reference's own known-answer NMS tests (``tests/test_nms.py:17-50``).
 """
 from __future__ import annotations
 

@@ -45,7 +45,7 @@ def pytest_collection_modifyitems(config, items):
 def golden_names():
     """Fixtures of the attention operator (made by the reference's PyTorch implementation)."""
     return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz"))
-                  if not os.path.basename(p).startswith("dcnv4_"))
+                  if not os.path.basename(p).startswith(("dcnv4_", "roi_align3d_", "nms3d_")))
 
 
 def dcnv4_golden_names():
@@ -99,3 +99,13 @@ def fda_env():
         else:
             os.environ[name] = old
     capi.reload_config()
+
+
+def detection_golden(prefix):
+    """Fixtures of ROI-Align 3D (``roi_align3d_``) or NMS 3D (``nms3d_``), made by the reference's CUDA kernels
+    (tests/golden/make_golden_detection.py): ``[(name, dict of numpy arrays)]``."""
+    out = []
+    for path in sorted(glob.glob(os.path.join(GOLDEN_DIR, prefix + "*.npz"))):
+        z = np.load(path)
+        out.append((os.path.basename(path)[:-4], {k: z[k] for k in z.files}))
+    return out

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import ops3d
+from conftest import detection_golden
 from ops3d import _C
 from oracle import detection_oracle as oracle
 
@@ -96,3 +97,20 @@ def test_roi_align_module_and_binding_contract():
     assert abs(grad_in.sum().item() - out.numel()) <= 1e-3  # interpolation weights of in-range samples sum to one
     with pytest.raises(RuntimeError):
         _C.roi_align_3d_forward(feats, rois[:, :6].contiguous(), out, 2, 2, 2, 1.0, 2, 1)
+
+
+@pytest.mark.parametrize("name,z", detection_golden("roi_align3d_"), ids=lambda v: v if isinstance(v, str) else "")
+def test_roi_align3d_matches_reference_kernel_fixtures(name, z):
+    size = tuple(int(v) for v in z["output_size"])
+    scale, ratio, order = float(z["spatial_scale"]), int(z["sampling_ratio"]), int(z["order"])
+    feats = torch.from_numpy(z["features"]).cuda().requires_grad_(True)
+    out = ops3d.roi_align_3d(feats, torch.from_numpy(z["rois"]).cuda(), size, scale, ratio, order)
+    out.backward(torch.from_numpy(z["grad_out"]).cuda())
+    assert np.abs(out.detach().cpu().numpy() - z["out"]).max() <= 1e-5
+    assert np.abs(feats.grad.cpu().numpy() - z["grad_features"]).max() <= 1e-4
+
+
+@pytest.mark.parametrize("name,z", detection_golden("nms3d_"), ids=lambda v: v if isinstance(v, str) else "")
+def test_nms3d_matches_reference_kernel_fixtures(name, z):
+    keep = _C.nms_3d(torch.from_numpy(z["boxes"]).cuda(), torch.from_numpy(z["scores"]).cuda(), float(z["threshold"]))
+    assert keep.cpu().tolist() == z["keep"].tolist()

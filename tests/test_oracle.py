@@ -139,3 +139,25 @@ def test_dcnv4_oracle_matches_reference_kernel_outputs():
             assert (goff - g["grad_offset"]).abs().max().item() <= 2e-5 * max(1.0, g["grad_offset"].abs().max().item())
             pinned_softmax_backward |= g["args"][-1]
     assert pinned_softmax_backward
+
+
+def test_detection_oracles_match_reference_kernel_outputs():
+    """ROI-Align 3D and NMS 3D oracles against what the reference's own CUDA kernels produced on a B200."""
+    import numpy as np
+
+    from conftest import detection_golden
+    from oracle import detection_oracle as o
+
+    rois = detection_golden("roi_align3d_")
+    assert len(rois) >= 3 and {int(z["order"]) for _, z in rois} == {0, 1}
+    for name, z in rois:
+        size = tuple(int(v) for v in z["output_size"])
+        scale, ratio, order = float(z["spatial_scale"]), int(z["sampling_ratio"]), int(z["order"])
+        out = o.roi_align3d_forward(z["features"], z["rois"], size, scale, ratio, order)
+        grad = o.roi_align3d_backward(z["grad_out"], z["rois"], z["features"].shape, scale, ratio, order)
+        assert np.abs(out - z["out"]).max() <= 2e-6, name
+        assert np.abs(grad - z["grad_features"]).max() <= 5e-6, name
+    nms = detection_golden("nms3d_")
+    assert len(nms) >= 3
+    for name, z in nms:
+        assert o.nms3d(z["boxes"], z["scores"], float(z["threshold"])) == z["keep"].tolist(), name
