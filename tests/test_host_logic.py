@@ -54,6 +54,12 @@ def test_reference_import_lines_resolve():
     assert F1 is FlashDeformAttnFunction and F2 is FlashDeformAttnFunction
     assert C1 is ops3d_b200._C and importlib.import_module("ops3d._C") is C1
     assert hasattr(C1, "flash_deform_attn_forward") and hasattr(C1, "flash_deform_attn_backward")
+    # the rest of the reference's binding (reference tests/test_extension.py:16-24, csrc/vision.cpp:15-21)
+    for name in ("nms_3d", "roi_align_3d_forward", "roi_align_3d_backward", "dcnv4_forward", "dcnv4_backward"):
+        assert hasattr(C1, name), name
+    from ops3d import RoIAlign, RoIAlign3DFunction, nms_nd, roi_align_3d  # reference ops3d/__init__.py:8-25
+
+    assert callable(nms_nd) and callable(roi_align_3d) and RoIAlign((2, 2, 2), 1.0).dim == 3 and RoIAlign3DFunction is not None
     assert fs is findspec and fsb is findspec_bwd
     assert factors(12) == [1, 2, 3, 4, 6, 12] and factors(1) == [1] and factors(49) == [1, 7, 49]
 
