@@ -551,6 +551,8 @@ def run_ours(args, cfg):
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
+    per_step = sorted(e[0].elapsed_time(e[3]) for e in events)   # each step on its own (launch gaps between steps excluded)
+    step_median, step_min = statistics.median(per_step), per_step[0]
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in events) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in events) / args.steps
     tail_ms = sum(e[2].elapsed_time(e[3]) for e in events) / args.steps
@@ -656,6 +658,7 @@ def run_ours(args, cfg):
         line = {
             "metric": METRIC, "value": B / (ms_per_step * 1e-3), "fwd_value": B / (fwd_ms * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "ms_per_step_median": step_median, "ms_per_step_min": step_min,   # rank 0's own steps
             "ms_fwd": fwd_ms, "ms_bwd_kernel": bwd_ms, "ms_reduce_and_cast": tail_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 value / f32 offsets, f32 accumulate" if cfg["vdt"] == "bfloat16" else "f32",
