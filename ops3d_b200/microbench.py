@@ -5,6 +5,9 @@
     python -m ops3d_b200.microbench prepass    slab sorting of the largest level (fda_bin_count / scan / fill kernels)
     python -m ops3d_b200.microbench project    the layer's query projections + packing: one GEMM that writes the packed
                                                tensor (project_and_pack) against two GEMMs + fda_pack_kernel
+    python -m ops3d_b200.microbench dcnv4      DCNv4-3D forward + backward (3x3x3 stencil over a 32x64x64 volume, 8 groups x 32
+                                               channels, fp16), and the reference's own kernels beside it when
+                                               baseline/_ref/ops3d_ref_dcnv4.so has been built
     python -m ops3d_b200.microbench exchange   cross-GPU sum + cast (fda_peer_reduce_cast_kernel); a world of one
                                                on a single GPU, or under torch.distributed.run on several:
         python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
@@ -115,6 +118,49 @@ def bench_project(args, dev):
             "ms_fused_gemm": ms_f, "ms_two_gemms_plus_pack_kernel": ms_u, "speedup": ms_u / ms_f, "max_abs_difference": err}
 
 
+def bench_dcnv4(args, dev):
+    import importlib.util
+
+    B, size_in, G, Dg, K = 2, (32, 64, 64), 8, 32, 27
+    kernel, stride, pad, dilation = (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1)
+    dt = torch.float16
+    Q = size_in[0] * size_in[1] * size_in[2]
+    padded = -(-(G * K * 4) // 8) * 8
+    gen = torch.Generator(device=dev).manual_seed(0)
+    value = torch.randn(B, *size_in, G * Dg, generator=gen, device=dev).to(dt)
+    rows = torch.randn(B, *size_in, padded, generator=gen, device=dev).to(dt)
+    grad_out = torch.randn(B, *size_in, G * Dg, generator=gen, device=dev).to(dt)
+    cfg = (kernel, stride, pad, dilation, G, Dg, 1.0, 0, True)
+    ms_f = _time(lambda: capi.dcnv4_forward(value, rows, *cfg), args.steps, args.warmup)
+    ms_b = _time(lambda: capi.dcnv4_backward(value, rows, grad_out, *cfg), args.steps, args.warmup)
+    points = B * Q * G * K
+    gathered = points * 8 * Dg * 2           # upper bound: all 8 corners of every point in range
+    res = {"kernel": "dcnv4_forward_kernel / dcnv4_backward_kernel<f16>", "points": points, "ms_forward": ms_f, "ms_backward": ms_b,
+           "forward_gather_GBs": (gathered + rows.numel() * 2 + B * Q * G * Dg * 2) / ms_f / 1e6,
+           "backward_gather_scatter_GBs": (gathered * 3 + 2 * rows.numel() * 2 + B * Q * G * Dg * 2) / ms_b / 1e6}
+    lib = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "ops3d_ref_dcnv4.so")
+    if os.path.exists(lib):
+        try:
+            spec = importlib.util.spec_from_file_location("ops3d_ref_dcnv4", lib)
+            ref = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(ref)
+            d_stride = 8
+            block_thread = (Dg // d_stride) * G * 8   # 8 output cells per block (256 threads); Q is a multiple of 8
+            rf = lambda: ref.dcnv4_forward(value, rows, *kernel, *stride, *pad, *dilation, G, Dg, 1.0, 64, 0, d_stride,  # noqa: E731
+                                           block_thread, True)
+            rb = lambda: ref.dcnv4_backward(value, rows, *kernel, *stride, *pad, *dilation, G, Dg, 1.0, 64, grad_out, 0,  # noqa: E731
+                                            d_stride, block_thread, True)
+            res["reference_ms_forward"] = _time(rf, args.steps, args.warmup)
+            res["reference_ms_backward"] = _time(rb, args.steps, args.warmup)
+            res["speedup_forward"] = res["reference_ms_forward"] / ms_f
+            res["speedup_backward"] = res["reference_ms_backward"] / ms_b
+        except Exception as exc:  # noqa: BLE001
+            res["reference"] = f"unavailable: {type(exc).__name__}: {exc}"
+    else:
+        res["reference"] = "baseline/_ref/ops3d_ref_dcnv4.so not built (baseline/build_ref_cuda.sh <checkout> --dcnv4)"
+    return res
+
+
 def bench_exchange(args, dev, rank, world):
     import torch.distributed as dist
 
@@ -151,7 +197,7 @@ def bench_exchange(args, dev, rank, world):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["cast", "pack", "prepass", "project", "exchange"])
+    ap.add_argument("what", choices=["cast", "pack", "prepass", "project", "dcnv4", "exchange"])
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--mb", type=float, default=256.0, help="fp32 image size in MB (cast, exchange)")
@@ -174,6 +220,8 @@ def main():
         res = bench_prepass(args, dev)
     elif args.what == "project":
         res = bench_project(args, dev)
+    elif args.what == "dcnv4":
+        res = bench_dcnv4(args, dev)
     else:
         res = bench_exchange(args, dev, rank, world)
     if rank == 0:
