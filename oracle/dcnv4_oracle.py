@@ -16,9 +16,10 @@ CPU implementation of this operator):
 Parity pin: PINNED to outputs of the reference's own CUDA kernels.  ``tests/golden/dcnv4_*.npz`` were produced by
 ``tests/golden/make_golden_dcnv4.py`` on a B200 from the reference sources compiled unmodified
 (``baseline/build_ref_cuda.sh <checkout> --dcnv4``); ``tests/test_oracle.py`` checks this module against them:
-``out`` and ``grad_value`` in all five cases, ``grad_offset`` in four.  The fifth (soft-maxed masks, 16 channels per
-group) goes through the reference's ``backward_kernel_dcn_warp_primitive``, whose soft-max backward block is misplaced
-inside the outermost stencil loop (``csrc/cuda/dcnv4_col2im_cuda.cuh:520-533``) and writes garbage; the soft-max
+``out`` in all five cases, ``grad_value`` and ``grad_offset`` in four.  The fifth (soft-maxed masks, 16 channels per
+group) would go through the reference's ``backward_kernel_dcn_warp_primitive``, whose soft-max backward block is
+misplaced inside the outermost stencil loop (``csrc/cuda/dcnv4_col2im_cuda.cuh:520-533``): it writes garbage and stores
+past the end of ``grad_offset``, so the generator does not run the reference's backward on it; the soft-max
 backward is pinned instead by two cases with 48 channels per group, which take ``backward_kernel_dcn`` (``:225-237``).
 """
 from __future__ import annotations

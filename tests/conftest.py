@@ -55,11 +55,13 @@ def dcnv4_golden_names():
 
 def load_dcnv4_golden(name):
     z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
-    d = {k: torch.from_numpy(z[k]) for k in ("value", "offset", "grad_out", "out", "grad_value", "grad_offset")}
+    d = {k: torch.from_numpy(z[k]) for k in ("value", "offset", "grad_out", "out")}
+    d["backward_stored"] = bool(z["backward_stored"])   # False: the generator did not run the reference's backward
+    if d["backward_stored"]:
+        d.update({k: torch.from_numpy(z[k]) for k in ("grad_value", "grad_offset")})
     d["args"] = (tuple(int(v) for v in z["kernel"]), tuple(int(v) for v in z["stride"]), tuple(int(v) for v in z["pad"]),
                  tuple(int(v) for v in z["dilation"]), int(z["group"]), int(z["group_channels"]), float(z["offset_scale"]),
                  int(z["remove_center"]), bool(z["softmax"]))
-    d["grad_offset_usable"] = bool(z["grad_offset_usable"])
     return d
 
 

@@ -9,7 +9,7 @@ seeded fp32 inputs; inputs and outputs are stored so that ``tests/test_oracle.py
     python tests/golden/make_golden_dcnv4.py --out <dir>          (on a machine with a GPU and the built .so)
 
     value [B,D,H,W,G*Dg] f32, offset [B,Do,Ho,Wo,padded] f32, grad_out, config (ints / floats),
-    out, grad_value, grad_offset
+    out, backward_stored and, where that is 1, grad_value, grad_offset
 
 Only this script and the reference's binary are involved: nothing of this repository's kernels or oracle computes
 the stored outputs (the oracle module is used for its seeded input generator alone).  The reference supports
@@ -26,14 +26,16 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 
-# name, B, (Din,Hin,Win), G, Dg, stride, pad, dilation, remove_center, softmax, offset_scale, grad_offset usable
+# name, B, (Din,Hin,Win), G, Dg, stride, pad, dilation, remove_center, softmax, offset_scale, run the reference's backward
 #
 # The last column: with soft-maxed masks and a channel-lane count that divides 32, the reference takes
 # backward_kernel_dcn_warp_primitive, whose soft-max backward block sits INSIDE the outermost stencil loop
 # (csrc/cuda/dcnv4_col2im_cuda.cuh:520-533: it runs after every kernel_w step, sums cache entries that were never
-# written and advances the output pointer past the group's K mask slots), so its grad_offset is garbage (NaN / values
-# of neighbouring slots).  Those cases pin out and grad_value only; the soft-max backward is pinned by a case whose 12
-# channel lanes (48 channels / 4) select backward_kernel_dcn, where the block follows the loops (:225-237).
+# written and advances the output pointer by K each time, i.e. up to 2K floats past the group's mask slots -- for the
+# last group of the last cell that is past the end of grad_offset).  Its result is garbage and the store is out of
+# bounds, so the reference's backward is NOT run on such a case: it pins ``out`` only.  The soft-max backward is pinned
+# by the cases whose 12 channel lanes (48 channels / 4) select backward_kernel_dcn, where the block follows the loops
+# (:225-237).
 CASES = [
     ("dcnv4_k27_softmax", 2, (5, 6, 7), 4, 16, (1, 1, 1), (1, 1, 1), (1, 1, 1), 0, True, 0.37, False),
     ("dcnv4_k26_plain", 1, (6, 5, 8), 2, 32, (1, 1, 1), (1, 1, 1), (1, 1, 1), 1, False, 0.73, True),
@@ -55,24 +57,28 @@ def main():
     spec.loader.exec_module(ref)
     os.makedirs(args.out, exist_ok=True)
     kernel = (3, 3, 3)
-    for name, B, size_in, G, Dg, stride, pad, dilation, rc, softmax, scale, goff_ok in CASES:
+    for name, B, size_in, G, Dg, stride, pad, dilation, rc, softmax, scale, run_backward in CASES:
         value, rows, grad_out = gen.make_inputs(B, size_in, G, Dg, kernel, stride, pad, dilation, rc, seed=11)
         rows = gen.keep_positions_off_the_grid(rows, size_in, kernel, stride, pad, dilation, G, scale, rc)
         v, o, go = value.cuda(), rows.cuda(), grad_out.cuda()
         d_stride = 4                      # fp32: 16-byte transfers
         block_thread = (Dg // d_stride) * G   # one (batch, cell) per block: no block straddles two batch elements
         out = ref.dcnv4_forward(v, o, *kernel, *stride, *pad, *dilation, G, Dg, scale, 64, rc, d_stride, block_thread, softmax)
-        gv, goff = ref.dcnv4_backward(v, o, *kernel, *stride, *pad, *dilation, G, Dg, scale, 64, go, rc, d_stride, block_thread,
-                                      softmax)
-        torch.cuda.synchronize()
-        np.savez_compressed(
-            os.path.join(args.out, name + ".npz"), value=value.numpy(), offset=rows.numpy(), grad_out=grad_out.numpy(),
+        stored = dict(
+            value=value.numpy(), offset=rows.numpy(), grad_out=grad_out.numpy(),
             size_in=np.array(size_in), group=np.int64(G), group_channels=np.int64(Dg), kernel=np.array(kernel),
             stride=np.array(stride), pad=np.array(pad), dilation=np.array(dilation), remove_center=np.int64(rc),
-            softmax=np.int64(int(softmax)), offset_scale=np.float64(scale), grad_offset_usable=np.int64(int(goff_ok)),
-            out=out.cpu().numpy(), grad_value=gv.float().cpu().numpy(), grad_offset=goff.float().cpu().numpy())
-        print(f"{name}: out|max|={out.abs().max().item():.4f} grad_value|max|={gv.abs().max().item():.4f} "
-              f"grad_offset|max|={goff.abs().max().item():.4f}")
+            softmax=np.int64(int(softmax)), offset_scale=np.float64(scale), backward_stored=np.int64(int(run_backward)),
+            out=out.cpu().numpy())
+        if run_backward:
+            assert not (softmax and 32 % (Dg // d_stride) == 0), "the reference's warp-primitive soft-max backward stores out of bounds"
+            gv, goff = ref.dcnv4_backward(v, o, *kernel, *stride, *pad, *dilation, G, Dg, scale, 64, go, rc, d_stride,
+                                          block_thread, softmax)
+            stored.update(grad_value=gv.float().cpu().numpy(), grad_offset=goff.float().cpu().numpy())
+        torch.cuda.synchronize()
+        np.savez_compressed(os.path.join(args.out, name + ".npz"), **stored)
+        print(f"{name}: out|max|={out.abs().max().item():.4f}" + (
+            f" grad_value|max|={gv.abs().max().item():.4f} grad_offset|max|={goff.abs().max().item():.4f}" if run_backward else ""))
 
 
 if __name__ == "__main__":

@@ -64,8 +64,8 @@ def test_dcnv4_matches_reference_kernel_fixtures(name):
     gv, goff = capi.dcnv4_backward(v, o, go, kernel, stride, pad, dilation, G, Dg, scale, rc, softmax)
     torch.cuda.synchronize()
     assert (out.cpu() - g["out"]).abs().max().item() <= 1e-4 * max(1.0, g["out"].abs().max().item())
-    assert (gv.cpu() - g["grad_value"]).abs().max().item() <= 1e-4 * max(1.0, g["grad_value"].abs().max().item())
-    if g["grad_offset_usable"]:  # else: the reference's own result is garbage there (see the fixture generator)
+    if g["backward_stored"]:  # else: the reference's backward is not run on that case (see the fixture generator)
+        assert (gv.cpu() - g["grad_value"]).abs().max().item() <= 1e-4 * max(1.0, g["grad_value"].abs().max().item())
         assert (goff.cpu() - g["grad_offset"]).abs().max().item() <= 1e-4 * max(1.0, g["grad_offset"].abs().max().item())
 
 

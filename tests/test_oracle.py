@@ -122,8 +122,8 @@ def test_detection_oracles_known_answers():
 
 def test_dcnv4_oracle_matches_reference_kernel_outputs():
     """The DCNv4-3D oracle against what the reference's own CUDA kernels produced on a B200 (fp32; fixtures and their
-    generator in tests/golden/).  ``grad_offset`` is skipped where the fixture marks it unusable (a defect of the
-    reference's warp-primitive soft-max backward, see the generator)."""
+    generator in tests/golden/).  One case stores the forward only: the reference's backward is not run on it (a defect
+    of its warp-primitive soft-max backward, see the generator); the soft-max backward is pinned by the other cases."""
     from conftest import dcnv4_golden_names, load_dcnv4_golden
     from oracle import dcnv4_oracle as o
 
@@ -134,8 +134,8 @@ def test_dcnv4_oracle_matches_reference_kernel_outputs():
         g = load_dcnv4_golden(name)
         out, gv, goff = o.dcnv4_forward_backward(g["value"], g["offset"], g["grad_out"], *g["args"])
         assert (out - g["out"]).abs().max().item() <= 2e-5 * max(1.0, g["out"].abs().max().item())
-        assert (gv - g["grad_value"]).abs().max().item() <= 2e-5 * max(1.0, g["grad_value"].abs().max().item())
-        if g["grad_offset_usable"]:
+        if g["backward_stored"]:
+            assert (gv - g["grad_value"]).abs().max().item() <= 2e-5 * max(1.0, g["grad_value"].abs().max().item())
             assert (goff - g["grad_offset"]).abs().max().item() <= 2e-5 * max(1.0, g["grad_offset"].abs().max().item())
             pinned_softmax_backward |= g["args"][-1]
     assert pinned_softmax_backward
