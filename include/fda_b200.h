@@ -111,6 +111,20 @@ size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int h
                                   int num_points, int packed_dtype);
 
 /*
+ * The cell-sorted backward (all points sorted by the cell they fall in; gathers and reductions once per run of equal
+ * cells instead of once per point) applies to 16-bit values with 32 channels per head and enough points to pay for
+ * its extra launches (FDA_BWD_SORT: 0 off, 1 by size, 2 always).  It needs more scratch than the slab-binned path:
+ * fda_backward_sorted_scratch_bytes() (0 when it does not apply).  A caller that wants whichever path the library
+ * prefers passes max(fda_backward_scratch_bytes, fda_backward_sorted_scratch_bytes) bytes; fda_backward_workspace_bytes
+ * already includes it.  fda_backward_path tells which path such a call takes: 0 the plain scatter kernel, 1 the
+ * slab-binned path for the largest level, 2 the cell-sorted path.  No counterpart in the reference.
+ */
+size_t fda_backward_sorted_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
+                                         int num_points, int value_dtype);
+int fda_backward_path(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query, int num_points,
+                      int value_dtype);
+
+/*
  * The library reads its tuning knobs (FDA_* environment variables) once, when it is loaded;
  * fda_reload_config re-reads them.  Not thread-safe against concurrent launches.
  */

@@ -16,7 +16,7 @@ DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 EXPORTS = (
     "fda_status_string", "fda_last_cuda_error", "fda_version", "fda_forward",
-    "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
+    "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward_sorted_scratch_bytes", "fda_backward_path", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
     "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
     "fda_pack_sampling", "fda_pack_sampling_backward", "fda_dcnv4_forward", "fda_dcnv4_backward",
@@ -61,6 +61,10 @@ def load() -> ctypes.CDLL:
     lib.fda_forward.restype = i
     lib.fda_backward_workspace_bytes.argtypes = [i] * 9
     lib.fda_backward_scratch_bytes.argtypes = [i] * 8
+    lib.fda_backward_path.argtypes = [i] * 8
+    lib.fda_backward_path.restype = i
+    lib.fda_backward_sorted_scratch_bytes.argtypes = [i] * 8
+    lib.fda_backward_sorted_scratch_bytes.restype = sz
     lib.fda_reload_config.restype = None
     lib.fda_group_reduce_cast.argtypes = [vp, i, i, vp, i, i, sz, i, vp]
     lib.fda_group_reduce_cast.restype = i
@@ -163,13 +167,30 @@ def scratch_bytes(value, packed, K) -> int:
     """Bytes of scratch for launches that hand work to one another (slab lists; fp32 logit-gradient plane for
     16-bit offsets)."""
     B, N, G, D = value.shape
-    return int(load().fda_backward_scratch_bytes(B, N, G, D, _levels(packed, K), packed.shape[1], K, DTYPE_CODE[packed.dtype]))
+    args = (B, N, G, D, _levels(packed, K), packed.shape[1], K)
+    return max(int(load().fda_backward_scratch_bytes(*args, DTYPE_CODE[packed.dtype])),
+               int(load().fda_backward_sorted_scratch_bytes(*args, DTYPE_CODE[value.dtype])))
 
 
 def binning_applies(value, packed, K) -> bool:
     """True when the slab-binned path handles the largest level of this problem (given scratch)."""
     B, N, G, D = value.shape
     return int(load().fda_backward_scratch_bytes(B, N, G, D, _levels(packed, K), packed.shape[1], K, 0)) > 0
+
+
+def backward_path(value, packed, K) -> int:
+    """0 plain scatter kernel, 1 slab-binned largest level, 2 cell-sorted (what a call with scratch takes)."""
+    B, N, G, D = value.shape
+    return int(load().fda_backward_path(B, N, G, D, _levels(packed, K), packed.shape[1], K, DTYPE_CODE[value.dtype]))
+
+
+def _scatter_launches(value, packed, K, first=True, last=True) -> int:
+    """Kernels of one scatter call that was given scratch: sorted = (count, 3 x scan, fill on the first launch of a
+    sequence) + walk (+ finalize on the last); binned = count, scan, fill, binned + plain; else the plain kernel."""
+    path = backward_path(value, packed, K)
+    if path == 2:
+        return (5 if first else 0) + 1 + (1 if last else 0)
+    return 5 if path == 1 else 1
 
 
 def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value=None, grad_packed=None,
@@ -191,8 +212,8 @@ def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value
             workspace.numel() * workspace.element_size() if workspace is not None else 0,
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype],
             im2col_step, 1, 0, _stream(value)))
-    # scatter kernel (+ count, scan, fill, binned kernels when the workspace includes binning scratch) + cast
-    _count(1 + (4 if binning_applies(value, packed, K) else 0) + (1 if value.dtype != torch.float32 else 0))
+    # scatter kernels (the workspace includes the scratch of the binned / sorted path when one applies) + cast
+    _count(_scatter_launches(value, packed, K) + (1 if value.dtype != torch.float32 else 0))
     return grad_value, grad_packed
 
 
@@ -223,8 +244,10 @@ def backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, g
             level_begin, level_end, flags,
             scratch.data_ptr() if scratch is not None else None,
             scratch.numel() * scratch.element_size() if scratch is not None else 0, _stream(value)))
-    binned_here = scratch is not None and binning_applies(value, packed, K) and not (flags & BWD_BINNED_DONE)
-    _count(1 + (4 if binned_here else 0))
+    if scratch is None or (flags & BWD_BINNED_DONE):
+        _count(1)
+    else:
+        _count(_scatter_launches(value, packed, K, first=not (flags & BWD_RESUME), last=bool(flags & BWD_FINALIZE)))
     return grad_packed
 
 

@@ -8,10 +8,12 @@
 #include <map>
 #include <mutex>
 #include <set>
+#include <type_traits>
 #include <utility>
 
 #include "fda_backward.cuh"
 #include "fda_backward_binned.cuh"
+#include "fda_backward_sorted.cuh"
 #include "fda_config.h"
 #include "fda_forward.cuh"
 
@@ -58,6 +60,10 @@ fda::Config read_config() {
     c.pair_rows = 1;
     c.forced_variant = 0;
     c.peer_reduce_blocks = 32;
+    c.sorted = 0;
+    c.sort_seg = 32;
+    c.sort_grid_x = 0;
+    c.sort_ahead = 4;
     if (const char *e = std::getenv("FDA_L2_KEEP_FRACTION")) c.l2_keep_fraction = std::atof(e);
     if (c.l2_keep_fraction < 0) c.l2_keep_fraction = 0;
     if (const char *e = std::getenv("FDA_BINNING")) c.binning = std::atoi(e) != 0;
@@ -71,6 +77,16 @@ fda::Config read_config() {
     }
     if (const char *e = std::getenv("FDA_PEER_REDUCE_BLOCKS")) c.peer_reduce_blocks = std::atoi(e);
     if (c.peer_reduce_blocks < 1) c.peer_reduce_blocks = 1;
+    if (const char *e = std::getenv("FDA_BWD_SORT")) c.sorted = std::atoi(e);
+    if (const char *e = std::getenv("FDA_SORT_SEGMENT")) c.sort_seg = std::atoi(e);
+    c.sort_seg = (c.sort_seg + 3) & ~3;
+    if (c.sort_seg < 4) c.sort_seg = 4;
+    if (c.sort_seg > 256) c.sort_seg = 256;
+    if (const char *e = std::getenv("FDA_SORT_GRID_X")) c.sort_grid_x = std::atoi(e);
+    if (c.sort_grid_x < 0) c.sort_grid_x = 0;
+    if (const char *e = std::getenv("FDA_SORT_AHEAD")) c.sort_ahead = std::atoi(e);
+    if (c.sort_ahead < 2) c.sort_ahead = 2;
+    if (c.sort_ahead > 4) c.sort_ahead = 4;
     return c;
 }
 
@@ -94,6 +110,22 @@ unsigned long long l2_keep_budget() {
         g_l2_bytes[dev].store(l2, std::memory_order_relaxed);
     }
     return (unsigned long long)(frac * (double)l2);
+}
+
+// Multiprocessors of the current device, looked up once per device (148 when there is no device).
+std::atomic<int> g_sm_count[kMaxDevices];
+int sm_count() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    int n = g_sm_count[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        g_sm_count[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
 }
 
 fda::Problem make_problem(const Shape &s) {
@@ -129,7 +161,7 @@ inline int padded_stride(int floats_per_row) {
 int ensure_smem(const void *kernel, size_t bytes) {
     static std::mutex mu;
     static std::set<std::pair<int, const void *>> done;
-    if (bytes <= 48 * 1024) return FDA_OK;
+    if (bytes + 1024 <= 48 * 1024) return FDA_OK;  // the kernels also have a little static shared memory
     if (bytes > 200 * 1024) return FDA_ERR_TOO_LARGE_STATIC;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -190,6 +222,53 @@ size_t bin_scratch_bytes(int B, int N, int G, int D, int Q, int K) {
 size_t dalpha_plane_bytes(int B, int G, int L, int Q, int K, int pdt) {
     if (pdt == FDA_DTYPE_F32 || B <= 0 || G <= 0 || L <= 0 || Q <= 0 || K <= 0) return 0;
     return round256((size_t)B * Q * G * L * K * sizeof(float));
+}
+
+// Cell-sorted backward: [counters [B*N*G]] [scan tile sums] [entries, 32 bytes per point] [positions, 4 bytes per
+// point] [results, 16 bytes per point].  Zero when the path is switched off or the problem does not qualify: 16-bit
+// values with 32 channels per head only (rows of four lanes, which is what the walk's matrix instructions assume);
+// point ids and list positions are 32-bit; FDA_BWD_SORT=1 wants at least a few million points, below that the extra
+// launches cost more than they save.
+struct SortLayout {
+    size_t counters, tile_sums, entries, positions, results, total;
+    unsigned long long bins, points;
+    unsigned int tiles;
+};
+SortLayout sort_layout(int B, int N, int G, int D, int L, int Q, int K, int vdt) {
+    SortLayout s;
+    std::memset(&s, 0, sizeof(s));
+    if (g_config.sorted <= 0) return s;
+    if (vdt == FDA_DTYPE_F32 || D != 32) return s;
+    if (B <= 0 || N <= 0 || G <= 0 || L <= 0 || Q <= 0 || K <= 0 || G >= 65536) return s;
+    const unsigned long long bins = (unsigned long long)B * N * G;
+    const unsigned long long points = (unsigned long long)B * Q * G * L * K;
+    if (bins >= (1ull << 31) || points >= (1ull << 31)) return s;
+    if (g_config.sorted == 1 && points < (4ull << 20)) return s;
+    s.bins = bins;
+    s.points = points;
+    s.tiles = (unsigned int)((bins + fda::kScanTile - 1) / fda::kScanTile);
+    s.counters = 0;
+    s.tile_sums = round256(bins * sizeof(unsigned int));
+    s.entries = s.tile_sums + round256((size_t)s.tiles * sizeof(unsigned int));
+    s.positions = s.entries + round256(points * 2 * sizeof(float4));
+    s.results = s.positions + round256(points * sizeof(unsigned int));
+    s.total = s.results + round256(points * sizeof(float4));
+    return s;
+}
+
+void attach_sorted(fda::Problem &p, const Shape &s, void *scratch, size_t scratch_bytes) {
+    if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 255u)) return;
+    const SortLayout lay = sort_layout(s.B, s.N, s.G, s.D, s.L, s.Q, s.K, s.vdt);
+    if (lay.total == 0 || scratch_bytes < lay.total) return;
+    char *base = static_cast<char *>(scratch);
+    p.sort_counters = reinterpret_cast<unsigned int *>(base + lay.counters);
+    p.sort_tile_sums = reinterpret_cast<unsigned int *>(base + lay.tile_sums);
+    p.sort_entries = reinterpret_cast<float4 *>(base + lay.entries);
+    p.sort_positions = reinterpret_cast<unsigned int *>(base + lay.positions);
+    p.sort_results = reinterpret_cast<float4 *>(base + lay.results);
+    p.sort_seg = g_config.sort_seg;
+    p.bin_allowed = 0;  // this layout replaces the binned one
+    p.dalpha = nullptr;
 }
 
 // Target size of one slab's share of the fp32 image.
@@ -279,8 +358,63 @@ int launch_binned_part(fda::Problem p, cudaStream_t st) {
     return launch_binned_slabs<VT, PT>(p, st);
 }
 
+// Cell-sorted path: the first launch of a sequence sorts the points of ALL levels; every launch walks the part of
+// the list that belongs to its levels; the last one writes grad_sampling_loc_attn.
+template <typename VT, typename PT>
+int launch_sorted(fda::Problem p, cudaStream_t st) {
+    if constexpr (std::is_same<VT, float>::value) {
+        return FDA_ERR_BAD_DTYPE;  // not reached: the layout is empty for fp32 values
+    } else {
+        const unsigned long long bins = (unsigned long long)p.B * p.N * p.G;
+        const unsigned int tiles = (unsigned int)((bins + fda::kScanTile - 1) / fda::kScanTile);
+        if (!p.resume) {
+            cudaError_t e = cudaMemsetAsync(p.sort_counters, 0, bins * sizeof(unsigned int), st);
+            if (e != cudaSuccess) return cuda_fail(e);
+            fda::Problem q = p;
+            q.row_stride = padded_stride(4 * p.LK);
+            const int threads = pick_threads(q, q.row_stride);
+            const size_t smem = (size_t)(threads >> q.gs_log2) * q.row_stride * sizeof(float);
+            auto count = fda::fda_sort_pass_kernel<PT, false>;
+            auto fill = fda::fda_sort_pass_kernel<PT, true>;
+            if (int rc = ensure_smem(reinterpret_cast<const void *>(count), smem)) return rc;
+            if (int rc = ensure_smem(reinterpret_cast<const void *>(fill), smem)) return rc;
+            count<<<row_grid(q, threads), threads, smem, st>>>(q);
+            fda::fda_scan_tile_sums_kernel<<<tiles, fda::kScanThreads, 0, st>>>(p.sort_counters, (size_t)bins, p.sort_tile_sums);
+            fda::fda_scan_spine_kernel<<<1, fda::kScanThreads, 0, st>>>(p.sort_tile_sums, tiles);
+            fda::fda_scan_apply_kernel<<<tiles, fda::kScanThreads, 0, st>>>(p.sort_counters, (size_t)bins, p.sort_tile_sums);
+            fill<<<row_grid(q, threads), threads, smem, st>>>(q);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return cuda_fail(e);
+        }
+        // shared memory of the walk: every warp's span of the list (32 bytes per entry) and every lane's ring of rows
+        constexpr int block = 128;
+        const int ahead = g_config.sort_ahead;
+        const size_t walk_smem = ((size_t)(block / 32) * 8 * (2 * (size_t)p.sort_seg + 1) + (size_t)ahead * fda::kWalkSlot * block) * 16;
+        int per_sm = (int)((size_t)227 * 1024 / (walk_smem + 1024));  // resident blocks: shared memory, then registers (3)
+        per_sm = per_sm > 3 ? 3 : (per_sm < 1 ? 1 : per_sm);
+        int gx = g_config.sort_grid_x;
+        if (gx <= 0) gx = (per_sm * sm_count() + p.B - 1) / p.B;
+        auto walk = ahead == 2 ? fda::fda_sorted_walk_kernel<VT, block, 3, 2>
+                               : (ahead == 3 ? fda::fda_sorted_walk_kernel<VT, block, 3, 3> : fda::fda_sorted_walk_kernel<VT, block, 3, 4>);
+        if (int rc = ensure_smem(reinterpret_cast<const void *>(walk), walk_smem)) return rc;
+        walk<<<dim3((unsigned)gx, (unsigned)p.B, 1), block, walk_smem, st>>>(p);
+        if (p.finalize) {
+            fda::Problem q = p;
+            q.row_stride = padded_stride(5 * p.LK);
+            const int threads = pick_threads(q, q.row_stride);
+            const size_t smem = (size_t)(threads >> q.gs_log2) * q.row_stride * sizeof(float);
+            auto fin = fda::fda_sort_finalize_kernel<PT>;
+            if (int rc = ensure_smem(reinterpret_cast<const void *>(fin), smem)) return rc;
+            fin<<<row_grid(q, threads), threads, smem, st>>>(q);
+        }
+        const cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? FDA_OK : cuda_fail(e);
+    }
+}
+
 template <typename VT, typename PT>
 int launch_backward(fda::Problem p, cudaStream_t st) {
+    if (p.sort_counters && !p.binned_elsewhere) return launch_sorted<VT, PT>(p, st);
     if (p.bin_allowed && !p.binned_elsewhere)
         if (int rc = launch_binned<VT, PT>(p, st)) return rc;
     p.row_stride = padded_stride(5 * p.LK);
@@ -362,13 +496,26 @@ size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int h
            dalpha_plane_bytes(batch, num_heads, num_levels, num_query, num_points, packed_dtype);
 }
 
+size_t fda_backward_sorted_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
+                                         int num_points, int value_dtype) {
+    return sort_layout(batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype).total;
+}
+
+int fda_backward_path(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query, int num_points,
+                      int value_dtype) {
+    if (sort_layout(batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype).total) return 2;
+    return bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points) ? 1 : 0;
+}
+
 size_t fda_backward_workspace_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
                                     int num_points, int value_dtype, int packed_dtype) {
     if (batch <= 0 || num_value <= 0 || num_heads <= 0 || head_dim <= 0) return 0;
     const size_t image = value_dtype == FDA_DTYPE_F32 ? 0 : round256((size_t)batch * num_value * num_heads * head_dim * sizeof(float));
     // fda_backward hands dalpha from launch to launch only when the largest level is slab-binned
     const size_t bin = bin_scratch_bytes(batch, num_value, num_heads, head_dim, num_query, num_points);
-    return image + (bin ? bin + dalpha_plane_bytes(batch, num_heads, num_levels, num_query, num_points, packed_dtype) : 0);
+    const size_t binned = bin ? bin + dalpha_plane_bytes(batch, num_heads, num_levels, num_query, num_points, packed_dtype) : 0;
+    const size_t sorted = sort_layout(batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype).total;
+    return image + (binned > sorted ? binned : sorted);
 }
 
 int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
@@ -400,6 +547,7 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
     p.finalize = (flags & FDA_BWD_FINALIZE) ? 1 : 0;
     // slab-binned handling of the largest level, when the caller gave scratch for it
     attach_scratch(p, s, scratch, scratch_bytes);
+    attach_sorted(p, s, scratch, scratch_bytes);
     p.binned_elsewhere = (flags & FDA_BWD_BINNED_DONE) ? 1 : 0;
     if (p.binned_elsewhere && !p.bin_allowed) return FDA_ERR_WORKSPACE;
     return FDA_DISPATCH(value_dtype, packed_dtype, (launch_backward<VT, PT>(p, st)));

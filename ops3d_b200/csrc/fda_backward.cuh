@@ -208,9 +208,9 @@ __device__ __forceinline__ void point_backward(const LevelGeom &lv, int GD, floa
     float gx, gy, gz;
     point_backward_geom<VT, kPair>(pg, a, lvl, acc_lvl, go, red_stride, active, gs, pol_v, pol_g, gx, gy, gz, da_out,
                                    acc_even, acc_odd);
-    gx_out = a * (float)lv.W * gx;
-    gy_out = a * (float)lv.H * gy;
-    gz_out = a * (float)lv.D * gz;
+    gx_out = a * lv.fW * gx;
+    gy_out = a * lv.fH * gy;
+    gz_out = a * lv.fD * gz;
 }
 
 template <typename VT, typename PT, bool kPair>

@@ -30,12 +30,12 @@ namespace fda {
 
 // brick (z-slab * ny + y-part) of a point from its normalised coordinates, or -1 when no corner lies inside the level
 __device__ __forceinline__ int slab_of_point(const LevelGeom &lv, const BinPlan &plan, float x, float y, float z) {
-    const float xf = floorf(unnormalize(x, (float)lv.W));
-    const float yf = floorf(unnormalize(y, (float)lv.H));
-    const float zf = floorf(unnormalize(z, (float)lv.D));
+    const float xf = floorf(unnormalize(x, lv.fW));
+    const float yf = floorf(unnormalize(y, lv.fH));
+    const float zf = floorf(unnormalize(z, lv.fD));
     // an axis has a corner in range iff floor in [-1, size-1]; written so that NaN fails
-    const bool ok = (xf >= -1.f) && (xf <= (float)(lv.W - 1)) && (yf >= -1.f) && (yf <= (float)(lv.H - 1)) &&
-                    (zf >= -1.f) && (zf <= (float)(lv.D - 1));
+    const bool ok = (xf >= -1.f) && (xf <= (lv.fW - 1.0f)) && (yf >= -1.f) && (yf <= (lv.fH - 1.0f)) &&
+                    (zf >= -1.f) && (zf <= (lv.fD - 1.0f));
     if (!ok) return -1;
     int z0 = (int)zf, y0 = (int)yf;
     z0 = z0 < 0 ? 0 : z0;
@@ -50,6 +50,7 @@ __device__ __forceinline__ LevelGeom level_geom_of(const Problem &p, int l) {
     lv.W = (int)p.shapes[3 * l + 2];
     lv.start = (int)p.lsi[l];
     lv.keep = 0;
+    lv.fD = (float)lv.D; lv.fH = (float)lv.H; lv.fW = (float)lv.W;
     return lv;
 }
 

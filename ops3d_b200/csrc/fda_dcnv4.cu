@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(fda::kThreads, 3) dcnv4_forward_kernel(const D
     }
     LevelGeom lv;
     lv.D = p.Din; lv.H = p.Hin; lv.W = p.Win; lv.start = 0; lv.keep = 0;
+    lv.fD = (float)p.Din; lv.fH = (float)p.Hin; lv.fW = (float)p.Win;
     const bool keep = (unsigned long long)p.Din * p.Hin * p.Win * p.GD * sizeof(T) <= p.l2_keep_bytes;
     const uint64_t pol = keep ? l2_policy_evict_last() : l2_policy_evict_normal();
     const int q = row_ok ? row / p.G : 0, g = row_ok ? row - q * p.G : 0;
@@ -179,6 +180,7 @@ __global__ void __launch_bounds__(fda::kThreads, 2) dcnv4_backward_kernel(const 
 
     LevelGeom lv;
     lv.D = p.Din; lv.H = p.Hin; lv.W = p.Win; lv.start = 0; lv.keep = 0;
+    lv.fD = (float)p.Din; lv.fH = (float)p.Hin; lv.fW = (float)p.Win;
     const size_t cells = (size_t)p.Din * p.Hin * p.Win;
     unsigned long long budget = p.l2_keep_bytes;
     const bool keep_image = cells * p.GD * 4ull <= budget;

@@ -31,6 +31,7 @@ struct LevelGeom {
     int D, H, W;
     int start;  // first cell of the level inside one batch element
     int keep;   // bit 0: keep this level's value rows in L2, bit 1: keep its fp32 gradient image in L2
+    float fD, fH, fW;  // the extents as floats (the kernels need them per point; the conversion is not free)
 };
 
 // Kernel parameter block (passed by value).
@@ -68,6 +69,15 @@ struct Problem {
     // fp32 plane [B][rows_per_b][LK] that carries raw dalpha from launch to launch (binned -> plain, level range ->
     // level range); null: the logit slots of grad_packed carry it (exact only when the packed dtype is fp32)
     float *dalpha;
+    // backward, cell-sorted handling of all levels (see fda_backward_sorted.cuh); null: not used
+    unsigned int *sort_counters;   // [B*N*G]: points per (batch, cell, head) -> exclusive scan -> end of each bin
+    unsigned int *sort_tile_sums;  // scratch of the scan
+    float4 *sort_entries;          // sorted list, 32 bytes per point: {voxel x, y, z inside the point's level, soft-max
+                                   // probability} {row b*Q*G + q*G + g, level | head << 4 | corner mask << 20, element
+                                   // offset of the base corner, 0}
+    unsigned int *sort_positions;  // [B*Q*G*L*K]: position of every point in the list (kNoPosition: no corner in range)
+    float4 *sort_results;          // per list position: {d/dx, d/dy, d/dz, dalpha}
+    int sort_seg;                  // list entries one lane group walks before it flushes its accumulators
 };
 
 constexpr int kMaxSlabs = 128;
@@ -354,6 +364,7 @@ __device__ __forceinline__ void build_level_table(LevelGeom *geom, const int64_t
         geom[l].W = (int)shapes[3 * l + 2];
         geom[l].start = (int)lsi[l];
         geom[l].keep = 0;
+        geom[l].fD = (float)geom[l].D; geom[l].fH = (float)geom[l].H; geom[l].fW = (float)geom[l].W;
         cells[l] = (unsigned long long)shapes[3 * l] * shapes[3 * l + 1] * shapes[3 * l + 2];
     }
     unsigned done = 0;
@@ -411,7 +422,7 @@ __device__ __forceinline__ int row_of_vector(int v, float inv_lk) { return (int)
 
 // From normalised coordinates in [0, 1] (the deformable-attention convention).
 __device__ __forceinline__ void point_geometry(const LevelGeom &lv, int GD, float x, float y, float z, PointGeom &pg) {
-    point_geometry_voxel(lv, GD, unnormalize(x, (float)lv.W), unnormalize(y, (float)lv.H), unnormalize(z, (float)lv.D), pg);
+    point_geometry_voxel(lv, GD, unnormalize(x, lv.fW), unnormalize(y, lv.fH), unnormalize(z, lv.fD), pg);
 }
 
 // Stage `nrows` consecutive packed rows (4*LK elements each, contiguous in global memory) into a
