@@ -60,10 +60,10 @@ fda::Config read_config() {
     c.pair_rows = 1;
     c.forced_variant = 0;
     c.peer_reduce_blocks = 32;
-    c.sorted = 0;
+    c.sorted = 1;
     c.sort_seg = 32;
     c.sort_grid_x = 0;
-    c.sort_ahead = 4;
+    c.sort_ahead = 2;  // 2 / 3 / 4 with 3 / 2 / 2 resident blocks: 31.2 / 33.8 / 33.5 ms per full-size backward
     if (const char *e = std::getenv("FDA_L2_KEEP_FRACTION")) c.l2_keep_fraction = std::atof(e);
     if (c.l2_keep_fraction < 0) c.l2_keep_fraction = 0;
     if (const char *e = std::getenv("FDA_BINNING")) c.binning = std::atoi(e) != 0;
@@ -243,7 +243,9 @@ SortLayout sort_layout(int B, int N, int G, int D, int L, int Q, int K, int vdt)
     const unsigned long long bins = (unsigned long long)B * N * G;
     const unsigned long long points = (unsigned long long)B * Q * G * L * K;
     if (bins >= (1ull << 31) || points >= (1ull << 31)) return s;
-    if (g_config.sorted == 1 && points < (4ull << 20)) return s;
+    // by size: a few million points at least (below that the five extra launches cost more than they save), and six
+    // points per (cell, head) on average -- the walk gathers and reduces once per RUN of equal cells, so it needs runs
+    if (g_config.sorted == 1 && (points < (4ull << 20) || (unsigned long long)Q * L * K < 6ull * N)) return s;
     s.bins = bins;
     s.points = points;
     s.tiles = (unsigned int)((bins + fda::kScanTile - 1) / fda::kScanTile);

@@ -104,27 +104,23 @@ __global__ void __launch_bounds__(kThreads) fda_sort_pass_kernel(const Problem p
         inv = 1.0f / s;
     }
     const size_t rowg = (size_t)b * p.rows_per_b + row;
-    // Eight points at a time: all position requests go out before the first answer is needed.
+    // Eight points at a time: all position requests go out before the first answer is needed.  Only the positions are
+    // kept across the two loops; recomputing a point's coordinates and tags is cheaper than the registers that would
+    // hold them (occupancy is what hides the latency of the requests).
     constexpr int kBatch = 8;
     for (int i0 = lane_c; i0 < LK; i0 += kBatch * gs) {
         unsigned int pos[kBatch];
-        SortTag tag[kBatch];
-        float xv[kBatch], yv[kBatch], zv[kBatch];
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
             const int i = i0 + u * gs;
             pos[u] = kNoPosition;
-            tag[u].ok = false;
             if (i < LK) {
-                const int l = (i >> 2) >> p.k_shift;
-                const LevelGeom lv = geom[l];
-                xv[u] = unnormalize(trow[3 * i], lv.fW);
-                yv[u] = unnormalize(trow[3 * i + 1], lv.fH);
-                zv[u] = unnormalize(trow[3 * i + 2], lv.fD);
-                tag[u] = sort_tag_of(lv, p.G, p.GD, g, xv[u], yv[u], zv[u]);
-                if (tag[u].ok) {
-                    if (kFill) pos[u] = atomicAdd(counters + tag[u].bin, 1u);
-                    else atomicAdd(counters + tag[u].bin, 1u);
+                const LevelGeom lv = geom[(i >> 2) >> p.k_shift];
+                const SortTag tag = sort_tag_of(lv, p.G, p.GD, g, unnormalize(trow[3 * i], lv.fW), unnormalize(trow[3 * i + 1], lv.fH),
+                                                unnormalize(trow[3 * i + 2], lv.fD));
+                if (tag.ok) {
+                    if (kFill) pos[u] = atomicAdd(counters + tag.bin, 1u);
+                    else atomicAdd(counters + tag.bin, 1u);
                 }
             }
         }
@@ -134,11 +130,16 @@ __global__ void __launch_bounds__(kThreads) fda_sort_pass_kernel(const Problem p
                 const int i = i0 + u * gs;
                 if (i < LK) {
                     if (pos[u] != kNoPosition) {
+                        const int l = (i >> 2) >> p.k_shift;
+                        const LevelGeom lv = geom[l];
+                        const float xv = unnormalize(trow[3 * i], lv.fW), yv = unnormalize(trow[3 * i + 1], lv.fH),
+                                    zv = unnormalize(trow[3 * i + 2], lv.fD);
+                        const SortTag tag = sort_tag_of(lv, p.G, p.GD, g, xv, yv, zv);
                         // one 32-byte record = one whole sector (no read-modify-write behind the store)
-                        const unsigned int meta = (unsigned int)((i >> 2) >> p.k_shift) | (g << 4) | (tag[u].in8 << 20);
+                        const unsigned int meta = (unsigned int)l | (g << 4) | (tag.in8 << 20);
                         float4 *rec = p.sort_entries + 2 * (size_t)pos[u];
-                        __stcs(rec, make_float4(xv[u], yv[u], zv[u], __expf(trow[3 * LK + i] - m) * inv));
-                        __stcs(rec + 1, make_float4(__uint_as_float((unsigned int)rowg), __uint_as_float(meta), __uint_as_float(tag[u].off0), 0.f));
+                        __stcs(rec, make_float4(xv, yv, zv, __expf(trow[3 * LK + i] - m) * inv));
+                        __stcs(rec + 1, make_float4(__uint_as_float((unsigned int)rowg), __uint_as_float(meta), __uint_as_float(tag.off0), 0.f));
                     }
                     p.sort_positions[rowg * (size_t)LK + i] = pos[u];
                 }

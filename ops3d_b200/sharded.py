@@ -231,7 +231,10 @@ class PeerReducer:
         nbytes = capi.scratch_bytes(value[:1], packed[:1], K)
         passes = self._level_passes(lsi)
         slab = None
-        if passes is not None and nbytes:
+        # the cell-sorted backward (when the library chooses it for this rank's rows) works level range by level range,
+        # not slab group by slab group
+        sorted_path = capi.backward_path(value[:1], packed[:1], K) == 2
+        if passes is not None and nbytes and not sorted_path:
             plan = capi.bin_plan(self.shapes_host, one, packed.shape[1], K)
             if plan is not None:
                 # Slab groups per level: more groups start the exchange earlier but add launches and barriers.
@@ -246,7 +249,7 @@ class PeerReducer:
         else:
             schedule = ("whole", None)
         # every rank must have arrived at the same pieces: compare a fingerprint across the group
-        flat = [len(schedule[0]), packed.shape[0], K, int(nbytes > 0)]  # query counts may differ by one between ranks
+        flat = [len(schedule[0]), packed.shape[0], K, int(nbytes > 0), int(sorted_path)]  # query counts may differ by one between ranks
         if schedule[0] == "slabs":
             flat += [slab[0]] + [v for r in slab[1] + slab[2] for v in r]
         elif schedule[0] == "levels":
