@@ -98,7 +98,7 @@ def measured_traffic(config_id):
 def make_device_inputs(cfg, dev, part, seed=0):
     """Seeded inputs of the configuration's shapes and distributions, generated on the device.
     Every rank generates the same full ``value`` (replicated) and the rows of its own partition
-    ``[part.b_begin:part.b_end, part.q_begin:part.q_end]``."""
+    ``[part.b_begin:part.b_end, part.q_begin:part.q_end]`` (of its own heads only under a head split)."""
     vdt = getattr(torch, cfg["vdt"])
     shapes = torch.tensor(cfg["shapes"], dtype=torch.long, device=dev)
     sizes = shapes.prod(1)
@@ -108,7 +108,9 @@ def make_device_inputs(cfg, dev, part, seed=0):
     nb, Qr = part.b_end - part.b_begin, part.q_end - part.q_begin
     gen = torch.Generator(device=dev).manual_seed(seed)
     value = torch.randn(B, N, G, D, generator=gen, device=dev, dtype=torch.float32).to(vdt)
-    gen_q = torch.Generator(device=dev).manual_seed(seed * 1000 + 17 + part.q_begin + 7919 * part.b_begin)
+    gen_q = torch.Generator(device=dev).manual_seed(seed * 1000 + 17 + part.q_begin + 7919 * part.b_begin + 104729 * part.h_begin)
+    if part.splits_heads:
+        G = part.h_end - part.h_begin   # rows of this rank's heads
     packed = torch.empty(nb, Qr, G, L * K * 4, device=dev, dtype=torch.float32)
     loc = packed[..., : L * K * 3]
     if cfg["coords"] == "uniform":
@@ -367,7 +369,7 @@ def parity_vs_unsharded(cfg, capi, dist, part, value, shapes, lsi, packed, grad_
     compares its out / grad_packed rows (exactly) and the reduced grad_value (2e-2 of the largest magnitude)."""
     K = cfg["K"]
     world = dist.get_world_size()
-    B, Q = cfg["B"], cfg["Q"]
+    B, Q, G, D = cfg["B"], cfg["Q"], cfg["G"], cfg["D"]
     nb, Qr = packed.shape[0], packed.shape[1]
     sizes = torch.tensor([nb, Qr], device=value.device)
     lo, hi = sizes.clone(), sizes.clone()
@@ -380,16 +382,21 @@ def parity_vs_unsharded(cfg, capi, dist, part, value, shapes, lsi, packed, grad_
         dist.all_gather_into_tensor(parts, t.contiguous())
         if part.kind == "queries":       # [R, B, Qr, ...] -> [B, R*Qr, ...]
             return parts.transpose(0, 1).reshape(B, world * Qr, *t.shape[2:]).contiguous()
+        if part.kind == "batch-heads":   # [B * size, 1, Q, Gr(, ...)] -> [B, Q, size * Gr(, ...)]: rank order is head order
+            size, gr = world // B, part.h_end - part.h_begin
+            per_head = t.shape[2:] if t.dim() == 4 else (gr, t.shape[2] // gr)   # [.., Gr, X] or [.., Gr*D]
+            full = parts.reshape(B, size, Q, *per_head).transpose(1, 2).reshape(B, Q, size * gr, *per_head[1:])
+            return (full if t.dim() == 4 else full.reshape(B, Q, -1)).contiguous()
         return parts.reshape(B, Q, *t.shape[2:])  # batch / batch-groups: rank order is row order
 
     pk_full, go_full = gather_full(packed), gather_full(grad_out)
     out_ref = capi.forward(value, shapes, lsi, pk_full, K)
     gv_ref, gp_ref = capi.backward(value, shapes, lsi, pk_full, go_full, K)
     torch.cuda.synchronize()
-    rows = (slice(part.b_begin, part.b_end), slice(part.q_begin, part.q_end))
+    from ops3d_b200.sharded import shard_rows
     tol = 1e-4 if cfg["vdt"] == "float32" else 2e-2
     errs, scales = {}, {}
-    for name, got, ref in (("out_rows", out, out_ref[rows]), ("grad_packed_rows", grad_packed, gp_ref[rows]),
+    for name, got, ref in (("out_rows", out, shard_rows(out_ref, part, G)), ("grad_packed_rows", grad_packed, shard_rows(gp_ref, part, G)),
                            ("grad_value", grad_value, gv_ref)):
         errs[name] = (got.float() - ref.float()).abs().max().item()
         scales[name] = ref.float().abs().max().item()
@@ -415,7 +422,7 @@ def run_ours(args, cfg):
 
     from ops3d_b200 import capi
     from ops3d_b200.host_stream import HostStreamedStep
-    from ops3d_b200.sharded import PeerReducer, partition
+    from ops3d_b200.sharded import PeerReducer, partition, shard_value
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -431,13 +438,14 @@ def run_ours(args, cfg):
     capi.load()
 
     B, Q, G, D, K = cfg["B"], cfg["Q"], cfg["G"], cfg["D"], cfg["K"]
-    part = partition(B, Q, rank, world)
+    part = partition(B, Q, rank, world, num_heads=G)
     nb, Qr = part.b_end - part.b_begin, part.q_end - part.q_begin
+    Gr = (part.h_end - part.h_begin) if part.splits_heads else G   # heads of this rank's rows
     value, shapes, lsi, packed, grad_out = make_device_inputs(cfg, dev, part)
-    value_local = value[part.b_begin:part.b_end]
+    value_local = shard_value(value, part)
     N = value.shape[1]
     vdt = value.dtype
-    out = torch.empty(nb, Qr, G * D, dtype=vdt, device=dev)
+    out = torch.empty(nb, Qr, Gr * D, dtype=vdt, device=dev)
     grad_packed = torch.empty_like(packed)
     use_peer = world > 1 and args.reduce == "peer"
     reducer, peer_note = None, None
@@ -455,15 +463,17 @@ def run_ours(args, cfg):
             reducer, use_peer = None, False
             peer_note = peer_note or "peer exchange unavailable on another rank; NCCL all-reduce used"
     L = len(cfg["shapes"])
-    grad_value = accum = scratch = None
+    grad_value = accum = scratch = accum_heads = None
     if not use_peer:
         n_scratch = capi.scratch_bytes(value_local, packed, K)
         scratch = torch.empty(n_scratch, dtype=torch.uint8, device=dev) if n_scratch else None
         grad_value = torch.empty_like(value)
         accum = torch.empty(value.shape, dtype=torch.float32, device=dev) if (vdt != torch.float32 or world > 1) else grad_value
+        accum_heads = torch.empty(value_local.shape, dtype=torch.float32, device=dev) if part.splits_heads else None
 
     def phase_forward():
-        capi.forward(value_local, shapes, lsi, packed, K, out=out)
+        # under a head split the compact copy of this rank's heads is part of the step (value changes every step)
+        capi.forward(shard_value(value, part) if part.splits_heads else value_local, shapes, lsi, packed, K, out=out)
 
     def phase_backward():
         nonlocal grad_value
@@ -473,6 +483,11 @@ def run_ours(args, cfg):
             return
         if world > 1:
             accum.zero_()   # the batch elements other ranks work on contribute zeros to the sum
+        if part.splits_heads:   # NCCL fallback under a head split: compact image, placed into the full one for the all-reduce
+            capi.backward_accumulate_levels(shard_value(value, part), shapes, lsi, packed, grad_out, K, accum_heads, grad_packed,
+                                            0, L, capi.BWD_ZERO_IMAGE | capi.BWD_FINALIZE, scratch=scratch)
+            accum[part.b_begin:part.b_end, :, part.h_begin:part.h_end] = accum_heads
+            return
         capi.backward_accumulate_levels(value_local, shapes, lsi, packed, grad_out, K, accum[part.b_begin:part.b_end],
                                         grad_packed, 0, L, (0 if world > 1 else capi.BWD_ZERO_IMAGE) | capi.BWD_FINALIZE,
                                         scratch=scratch)
@@ -580,18 +595,27 @@ def run_ours(args, cfg):
 
     # ---- byte model and roofline (this rank's launches; all ranks do equal work) ----------------------
     corners = count_in_range_corners(cfg, packed)
-    bm = byte_model(cfg, corners, nb, Qr, N)
+    bm = byte_model(dict(cfg, G=Gr), corners, nb, Qr, N)
 
     # ---- end to end: host buffers in, host buffers out, through the package's host-buffer entry point -
     e2e_ms, h2d, d2h, e2e_steps = None, 0, 0, 0
     if not args.no_e2e:
         e2e_steps = max(2, min(args.steps, 5))
+        if part.splits_heads:
+            # the host-buffer step streams query chunks: it runs on the query split of the batch groups, with rows and a
+            # reducer of its own
+            part_e = partition(B, Q, rank, world, mode="rows")
+            del packed, grad_out, out, grad_packed
+            _, _, _, packed, grad_out = make_device_inputs(cfg, dev, part_e)
+            out = torch.empty(packed.shape[0], packed.shape[1], G * D, dtype=vdt, device=dev)
+            grad_packed = None
+            reducer = PeerReducer(value.shape, vdt, dev, spatial_shapes=shapes, part=part_e) if use_peer else None
         host_value = value.cpu().pin_memory()
         host_packed, host_go = packed.cpu().pin_memory(), grad_out.cpu().pin_memory()
         host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
         host_gv = torch.empty(value.shape, dtype=vdt).pin_memory()
         host_gp = torch.empty(packed.shape, dtype=packed.dtype).pin_memory()
-        del out, grad_value, grad_packed, accum, scratch, value, value_local, packed, grad_out
+        del out, grad_value, grad_packed, accum, scratch, value, value_local, packed, grad_out, accum_heads
         torch.cuda.empty_cache()
         streamed = HostStreamedStep(host_value.shape, vdt, host_packed.shape, host_packed.dtype, K, shapes, lsi, dev,
                                     reducer=reducer)
@@ -651,10 +675,12 @@ def run_ours(args, cfg):
         if world > 1:
             how = {"batch": f"{nb} whole batch element(s) per rank (no cross-rank sum; finished images cast and broadcast)",
                    "batch-groups": f"{len(part.group)} ranks per batch element split its queries; partial fp32 images summed within the group",
+                   "batch-heads": f"{len(part.group)} ranks per batch element split its heads ({Gr} each): no sum, every rank "
+                                  "converts its finished slice of the image and stores it into every rank's grad_value",
                    "queries": f"queries of every batch element split over all {world} ranks"}[part.kind]
             sharding = (how + ", value replicated; exchange = " +
-                        ("fused peer-memory reduce+cast kernel pipelined with the scatter kernels" if use_peer
-                         else "NCCL all-reduce, then cast"))
+                        (("peer-memory cast+broadcast kernel" if part.splits_heads else "fused peer-memory reduce+cast kernel")
+                         + " pipelined with the backward kernels" if use_peer else "NCCL all-reduce, then cast"))
         line = {
             "metric": METRIC, "value": B / (ms_per_step * 1e-3), "fwd_value": B / (fwd_ms * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,

@@ -251,6 +251,18 @@ int fda_group_reduce_cast(const float *const *group_images, int group_size, int 
                           size_t num_elements, int value_dtype, void *stream);
 
 /*
+ * Head-sharded backward (every rank of a group owns a slice of the heads of one batch element, so no sum is needed):
+ * converts the cells [cell_begin, cell_begin + cell_count) of this rank's compact fp32 image [cells][slice_elements] to
+ * value_dtype and stores them into every rank's full gradient [cells][full_elements] at element offset
+ * head_offset_elements of each cell.  peer_outputs[r] points at the batch element inside rank r's grad_value (peer
+ * memory, 16-byte aligned); all element counts are multiples of 8.  No waits inside; run one cross-rank barrier after
+ * it before grad_value is read.  No counterpart in the reference.
+ */
+int fda_head_slice_cast_push(const float *image_slice, void *const *peer_outputs, int world, int rank,
+                             size_t cell_begin, size_t cell_count, int slice_elements, int full_elements,
+                             int head_offset_elements, int value_dtype, void *stream);
+
+/*
  * Push variant of the same exchange, in two calls with a cross-rank barrier between them (and the
  * usual one after): fda_peer_push_partials stores the slices of the local image that other ranks
  * own into their staging areas (peer_staging: HOST array of `world` DEVICE pointers, each area

@@ -21,7 +21,7 @@ EXPORTS = (
     "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
     "fda_pack_sampling", "fda_pack_sampling_backward", "fda_dcnv4_forward", "fda_dcnv4_backward",
     "fda_dcnv4_backward_workspace_bytes", "fda_dcnv4_output_size", "fda_roi_align3d_forward", "fda_roi_align3d_backward",
-    "fda_nms3d", "fda_nms3d_workspace_bytes", "fda_reload_config", "fda_group_reduce_cast",
+    "fda_nms3d", "fda_nms3d_workspace_bytes", "fda_reload_config", "fda_group_reduce_cast", "fda_head_slice_cast_push",
 )
 BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE = 1, 2, 4, 8
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
@@ -68,6 +68,8 @@ def load() -> ctypes.CDLL:
     lib.fda_reload_config.restype = None
     lib.fda_group_reduce_cast.argtypes = [vp, i, i, vp, i, i, sz, i, vp]
     lib.fda_group_reduce_cast.restype = i
+    lib.fda_head_slice_cast_push.argtypes = [vp, vp, i, i, sz, sz, i, i, i, i, vp]
+    lib.fda_head_slice_cast_push.restype = i
     lib.fda_backward_scratch_bytes.restype = sz
     lib.fda_backward_workspace_bytes.restype = sz
     lib.fda_backward.argtypes = [vp] * 8 + [sz] + [i] * 12 + [vp]
@@ -321,6 +323,18 @@ def group_reduce_cast(group_image_ptrs, group_rank, output_ptrs, rank, num_eleme
     with torch.cuda.device(device):
         check(load().fda_group_reduce_cast(imgs, gsize, group_rank, outs, world, rank, num_elements, DTYPE_CODE[dtype],
                                            torch.cuda.current_stream(device).cuda_stream))
+    _count(1)
+
+
+def head_slice_cast_push(image_ptr, output_ptrs, rank, cell_begin, cell_count, slice_elements, full_elements,
+                         head_offset_elements, dtype, device):
+    """``fda_head_slice_cast_push``: ``image_ptr`` = this rank's compact fp32 image of one batch element (int address),
+    ``output_ptrs`` = address of that batch element inside every rank's full gradient."""
+    world = len(output_ptrs)
+    outs = (ctypes.c_void_p * world)(*output_ptrs)
+    with torch.cuda.device(device):
+        check(load().fda_head_slice_cast_push(image_ptr, outs, world, rank, cell_begin, cell_count, slice_elements, full_elements,
+                                              head_offset_elements, DTYPE_CODE[dtype], torch.cuda.current_stream(device).cuda_stream))
     _count(1)
 
 

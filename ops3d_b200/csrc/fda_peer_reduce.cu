@@ -389,6 +389,64 @@ extern "C" int fda_group_reduce_cast(const float *const *group_images, int group
     return status_of(e);
 }
 
+// Head-sharded backward: every rank owns a slice of the heads of a batch element, so its fp32 image
+// [cells][slice] is already the final sum.  This kernel converts it to the value dtype and stores it into the slice's
+// place inside every rank's full grad_value [cells][full]: position (cell, head_offset + e) for e < slice.  Plain
+// peer stores, no waits; the caller runs one cross-rank barrier after it.
+template <typename VT>
+__global__ void __launch_bounds__(512) fda_head_slice_push_kernel(const float *__restrict__ image, const PeerPtrs pp, const int n_out,
+                                                                  size_t unit_begin, size_t unit_end, unsigned int slice_units,
+                                                                  unsigned int full_units, unsigned int head_units) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t u = unit_begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < unit_end; u += stride) {
+        const float4 *src = reinterpret_cast<const float4 *>(image + u * 8);
+        const float4 lo = __ldcs(src), hi = __ldcs(src + 1);
+        const float a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        const size_t cell = u / slice_units;
+        const size_t dst = cell * full_units + head_units + (u - cell * slice_units);  // 8-element unit inside the full tensor
+        for (int p = 0; p < n_out; ++p) Out8<VT>::store(pp.out[p], dst, a);
+    }
+}
+
+extern "C" int fda_head_slice_cast_push(const float *image_slice, void *const *peer_outputs, int world, int rank,
+                                        size_t cell_begin, size_t cell_count, int slice_elements, int full_elements,
+                                        int head_offset_elements, int value_dtype, void *stream) {
+    if (!image_slice || !peer_outputs) return FDA_ERR_NULL_POINTER;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return FDA_ERR_BAD_SHAPE;
+    if (value_dtype < 0 || value_dtype > 2) return FDA_ERR_BAD_DTYPE;
+    if (slice_elements <= 0 || full_elements < slice_elements || head_offset_elements < 0 ||
+        head_offset_elements + slice_elements > full_elements)
+        return FDA_ERR_BAD_SHAPE;
+    if (slice_elements % 8 || full_elements % 8 || head_offset_elements % 8) return FDA_ERR_BAD_SHAPE;
+    if (reinterpret_cast<uintptr_t>(image_slice) & 15u) return FDA_ERR_MISALIGNED;
+    PeerPtrs pp;
+    for (int p = 0; p < kMaxPeers; ++p) { pp.img[p] = nullptr; pp.out[p] = nullptr; }
+    for (int p = 0; p < world; ++p) {
+        const int r = (rank + p) % world;  // local copy first
+        if (!peer_outputs[r]) return FDA_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(peer_outputs[r]) & 15u) return FDA_ERR_MISALIGNED;
+        pp.out[p] = peer_outputs[r];
+    }
+    if (cell_count == 0) return FDA_OK;
+    const unsigned int su = (unsigned int)slice_elements / 8u;
+    const size_t ub = cell_begin * su, ue = (cell_begin + cell_count) * su;
+    int blocks = fda::config().peer_reduce_blocks;
+    const size_t need = (ue - ub + 511) / 512;
+    if ((size_t)blocks > need) blocks = (int)need;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (value_dtype == FDA_DTYPE_F32)
+        fda_head_slice_push_kernel<float><<<blocks, 512, 0, st>>>(image_slice, pp, world, ub, ue, su, (unsigned int)full_elements / 8u,
+                                                                  (unsigned int)head_offset_elements / 8u);
+    else if (value_dtype == FDA_DTYPE_F16)
+        fda_head_slice_push_kernel<__half><<<blocks, 512, 0, st>>>(image_slice, pp, world, ub, ue, su, (unsigned int)full_elements / 8u,
+                                                                   (unsigned int)head_offset_elements / 8u);
+    else
+        fda_head_slice_push_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(image_slice, pp, world, ub, ue, su,
+                                                                          (unsigned int)full_elements / 8u,
+                                                                          (unsigned int)head_offset_elements / 8u);
+    return status_of(cudaGetLastError());
+}
+
 extern "C" int fda_peer_reduce_cast(const float *const *peer_images, void *const *peer_outputs, int world, int rank,
                                     size_t num_elements, int value_dtype, void *stream) {
     // every rank holds a partial image: the group is the whole job

@@ -50,6 +50,9 @@ class HostStreamedStep:
         self.nb, self.Q, self.device = nb, Q, device
         self.shapes, self.lsi = shapes, level_start_index
         self.reducer = reducer
+        if reducer is not None and reducer.part.splits_heads:
+            raise ValueError("HostStreamedStep streams query chunks: build the reducer on a partition that splits "
+                             "queries, not heads (partition(..., mode='rows'))")
         self.b_begin = reducer.part.b_begin if reducer is not None else 0
         if reducer is None and nb != B:
             raise ValueError("without a reducer the rows must cover every batch element")

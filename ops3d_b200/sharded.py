@@ -12,8 +12,13 @@ scatters into and exchanges the image of ONE batch element (or of whole batch el
 
 * ``world`` divides ``B``: every rank owns ``B / world`` whole batch elements -- no sum at all, the
   exchange is a cast + broadcast of finished images;
-* ``B`` divides ``world``: the ``world / B`` ranks of a group split the queries of one batch element
-  and sum only among themselves;
+* ``B`` divides ``world`` and ``world / B`` divides the number of heads: the ranks of a group split the HEADS of
+  one batch element ("batch-heads").  A head's rows read and write only that head's channels of ``value`` /
+  ``grad_value``, so the group needs no sum either -- every rank converts its finished slice of the image and
+  stores it into every rank's ``grad_value`` -- and a rank sees every query, so the density of sampling points
+  per cell that the cell-sorted backward lives on does not drop with the number of ranks;
+* ``B`` divides ``world`` otherwise: the ``world / B`` ranks of a group split the queries of one batch element
+  and sum only among themselves ("batch-groups"; ``FDA_PARTITION=rows`` prefers this over the head split);
 * otherwise the queries of every batch element are split over all ranks (every rank touches every
   image; ``FDA_PARTITION=queries`` forces this arrangement).
 
@@ -46,38 +51,71 @@ def query_range(num_query: int, rank: int, world: int) -> Tuple[int, int]:
 
 class Partition(NamedTuple):
     """This rank's share of the ``[B, Q]`` rows: batch elements ``[b_begin, b_end)``, queries
-    ``[q_begin, q_end)`` of each of them, and the ranks that share those batch elements (``group``, in
-    rank order; this rank is ``group[group_rank]``)."""
+    ``[q_begin, q_end)`` of each of them, heads ``[h_begin, h_end)`` (``0, 0``: all heads), and the ranks that share
+    those batch elements (``group``, in rank order; this rank is ``group[group_rank]``)."""
     b_begin: int
     b_end: int
     q_begin: int
     q_end: int
     group: Tuple[int, ...]
     group_rank: int
-    kind: str  # "batch" (whole batch elements), "batch-groups" (one element per group), "queries"
+    kind: str  # "batch" (whole batch elements), "batch-heads" / "batch-groups" (one element per group), "queries"
+    h_begin: int = 0
+    h_end: int = 0
+
+    @property
+    def splits_heads(self) -> bool:
+        return self.h_end > self.h_begin
 
 
-def partition(num_batch: int, num_query: int, rank: int, world: int, mode: Optional[str] = None) -> Partition:
+def partition(num_batch: int, num_query: int, rank: int, world: int, mode: Optional[str] = None,
+              num_heads: Optional[int] = None) -> Partition:
+    """``mode`` (default: ``FDA_PARTITION``, else "auto"): "auto", "rows" (auto, but never split heads) or "queries".
+    ``num_heads`` makes the head split available to "auto"."""
     if not (0 <= rank < world):
         raise ValueError(f"rank {rank} outside world of {world}")
     mode = mode or os.environ.get("FDA_PARTITION", "auto")
-    if mode not in ("auto", "queries"):
-        raise ValueError(f"FDA_PARTITION must be 'auto' or 'queries', got {mode!r}")
-    if mode == "auto" and world > 1 and num_batch % world == 0:
+    if mode not in ("auto", "rows", "queries"):
+        raise ValueError(f"FDA_PARTITION must be 'auto', 'rows' or 'queries', got {mode!r}")
+    if mode != "queries" and world > 1 and num_batch % world == 0:
         per = num_batch // world
         return Partition(rank * per, (rank + 1) * per, 0, num_query, (rank,), 0, "batch")
-    if mode == "auto" and world > 1 and world % num_batch == 0:
+    if mode != "queries" and world > 1 and world % num_batch == 0:
         size = world // num_batch
         b, sub = divmod(rank, size)
+        group = tuple(range(b * size, (b + 1) * size))
+        if mode == "auto" and num_heads and num_heads % size == 0:
+            per = num_heads // size
+            return Partition(b, b + 1, 0, num_query, group, sub, "batch-heads", sub * per, (sub + 1) * per)
         qb, qe = query_range(num_query, sub, size)
-        return Partition(b, b + 1, qb, qe, tuple(range(b * size, (b + 1) * size)), sub, "batch-groups")
+        return Partition(b, b + 1, qb, qe, group, sub, "batch-groups")
     qb, qe = query_range(num_query, rank, world)
     return Partition(0, num_batch, qb, qe, tuple(range(world)), rank, "queries")
 
 
-def shard_rows(t: torch.Tensor, part: Partition) -> torch.Tensor:
-    """This rank's rows of a full ``[B, Q, ...]`` tensor, contiguous: ``[b_end-b_begin, q_end-q_begin, ...]``."""
-    return t[part.b_begin:part.b_end, part.q_begin:part.q_end].contiguous()
+def shard_rows(t: torch.Tensor, part: Partition, num_heads: Optional[int] = None) -> torch.Tensor:
+    """This rank's rows of a full ``[B, Q, ...]`` tensor, contiguous: ``[b_end-b_begin, q_end-q_begin, ...]``.
+    With a head split, dimension 2 of a 4-D tensor ``[B, Q, G, ...]`` is cut to the rank's heads, and a 3-D tensor
+    ``[B, Q, G*D]`` is cut as ``[B, Q, G, D]`` (``num_heads`` = G required)."""
+    rows = t[part.b_begin:part.b_end, part.q_begin:part.q_end]
+    if part.splits_heads:
+        if rows.dim() == 4:
+            rows = rows[:, :, part.h_begin:part.h_end]
+        elif rows.dim() == 3:
+            if not num_heads or rows.shape[2] % num_heads:
+                raise ValueError("shard_rows: a [B, Q, G*D] tensor under a head split needs num_heads")
+            rows = rows.reshape(rows.shape[0], rows.shape[1], num_heads, -1)[:, :, part.h_begin:part.h_end]
+            rows = rows.reshape(rows.shape[0], rows.shape[1], -1)
+        else:
+            raise ValueError("shard_rows: expected [B, Q, G, ...] or [B, Q, G*D] under a head split")
+    return rows.contiguous()
+
+
+def shard_value(value: torch.Tensor, part: Partition) -> torch.Tensor:
+    """The part of ``value [B, N, G, D]`` this rank's rows read: its batch elements, and under a head split its heads
+    (a compact copy)."""
+    v = value[part.b_begin:part.b_end]
+    return v[:, :, part.h_begin:part.h_end].contiguous() if part.splits_heads else v
 
 
 def shard_queries(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -151,7 +189,9 @@ class PeerReducer:
         B = self.shape[0]
         self.part = part if part is not None else partition(B, 0, self.rank, self.world)
         self.nb = self.part.b_end - self.part.b_begin   # batch elements this rank works on (same on every rank)
-        self.image = symm_mem.empty(self.nb, *self.shape[1:], dtype=torch.float32, device=device)
+        self.heads = self.part.splits_heads              # this rank's image is a finished slice: no sum, only a broadcast
+        self.gr = (self.part.h_end - self.part.h_begin) if self.heads else self.shape[2]   # heads of this rank's image
+        self.image = symm_mem.empty(self.nb, self.shape[1], self.gr, self.shape[3], dtype=torch.float32, device=device)
         self.out = symm_mem.empty(*self.shape, dtype=dtype, device=device)
         self.h_image = symm_mem.rendezvous(self.image, self.group)
         self.h_out = symm_mem.rendezvous(self.out, self.group)
@@ -162,7 +202,7 @@ class PeerReducer:
         self.mc_out = int(getattr(self.h_out, "multicast_ptr", 0) or 0)
         mode = os.environ.get("FDA_PEER_REDUCE_MODE", "auto")  # auto | multimem | p2p (pull) | push
         whole_job = len(self.part.group) == self.world and self.nb == B
-        if mode in ("multimem", "push") and not whole_job:
+        if mode in ("multimem", "push") and (not whole_job or self.heads):
             raise RuntimeError(f"FDA_PEER_REDUCE_MODE={mode} needs the 'queries' partition (FDA_PARTITION=queries)")
         # Measured on 8 x B200: standing alone the in-switch reduction is the faster exchange (3.7 vs 4.4 ms
         # for a 1.22 GB image), but overlapped with the slab-binned backward it is the slower one (step
@@ -203,7 +243,7 @@ class PeerReducer:
             return None
         cells = [int(c) for c in cells_t.tolist()]
         L = len(cells)
-        gd = self.shape[2] * self.shape[3]
+        gd = self.gr * self.shape[3]
         if L < 2 or sum(cells) != self.shape[1]:
             return None
         big = max(range(L), key=lambda l: cells[l])
@@ -227,7 +267,7 @@ class PeerReducer:
         key = (tuple(packed.shape), packed.dtype, K, lsi.data_ptr(), lsi._version)
         if key == self._schedule_key:
             return
-        one = (1,) + tuple(value.shape[1:])
+        one = (1,) + tuple(value.shape[1:])   # `value` is this rank's part (shard_value): compact under a head split
         nbytes = capi.scratch_bytes(value[:1], packed[:1], K)
         passes = self._level_passes(lsi)
         slab = None
@@ -241,7 +281,7 @@ class PeerReducer:
                 # Measured with the batch-aligned partition on 8 GPUs (4 ranks per batch element): 1 / 2 / 4 / 8
                 # groups give 7.69 / 7.80 / 8.07 / 8.58 ms per step; on 2 GPUs 1 / 2 / 4 groups 27.7 / 27.9 / 28.1 ms.
                 parts = max(1, int(os.environ.get("FDA_SLAB_PARTS", "1")))
-                slab = slab_exchange_ranges(self.shapes_host, self.shape, plan, parts)
+                slab = slab_exchange_ranges(self.shapes_host, one, plan, parts)
         if slab is not None:
             schedule = ("slabs", slab)
         elif passes is not None:
@@ -274,6 +314,19 @@ class PeerReducer:
         from . import capi
 
         out_elem = self.out.element_size()
+        if self.heads:
+            # this rank's slice of the image is final: convert it and store it into every rank's grad_value
+            slice_elems, full_elems = self.gr * self.shape[3], self.shape[2] * self.shape[3]
+            if elem_begin % slice_elems or elem_count % slice_elems:
+                raise RuntimeError("head-sharded exchange: a piece must consist of whole cells")
+            batch_off = (self.part.b_begin + local_b) * self.shape[1] * full_elems * out_elem
+            self.h_image.barrier(channel=0)   # nobody still reads the grad_value of the previous backward
+            capi.head_slice_cast_push(self.image_ptrs[self.rank] + local_b * self.per_batch * 4,
+                                      [p + batch_off for p in self.out_ptrs], self.rank, elem_begin // slice_elems,
+                                      elem_count // slice_elems, slice_elems, full_elems, self.part.h_begin * self.shape[3],
+                                      self.dtype, self.device)
+            self.h_out.barrier(channel=0)     # every rank's slices have landed
+            return
         img_off = (local_b * self.per_batch + elem_begin) * 4
         out_off = ((self.part.b_begin + local_b) * self.per_batch + elem_begin) * out_elem
         if self.use_push:
@@ -300,6 +353,7 @@ class PeerReducer:
 
         if tuple(value.shape) != self.shape or value.dtype != self.dtype:
             raise ValueError("PeerReducer was built for another value shape / dtype")
+        value = shard_value(value, self.part)   # [nb, N, heads of this rank, D]
         if packed.shape[0] != self.nb or grad_out.shape[0] != self.nb:
             raise ValueError(f"this rank works on {self.nb} batch element(s), got rows for {packed.shape[0]}")
         L = shapes.shape[0]
@@ -312,7 +366,6 @@ class PeerReducer:
         main.wait_stream(self.side)  # the zero-fill issued after the previous backward is done
         zero = 0 if self._image_clean else capi.BWD_ZERO_IMAGE
         self._image_clean = False
-        b0 = self.part.b_begin
         scratch_of = (lambda lb: self._scratch[lb]) if self._scratch is not None else (lambda lb: None)
 
         def hand_over(lb, elem_begin, elem_count):
@@ -323,7 +376,7 @@ class PeerReducer:
                 self._exchange(lb, elem_begin, elem_count)
 
         def args_of(lb):
-            return (value[b0 + lb:b0 + lb + 1], shapes, lsi, packed[lb:lb + 1], grad_out[lb:lb + 1], K,
+            return (value[lb:lb + 1], shapes, lsi, packed[lb:lb + 1], grad_out[lb:lb + 1], K,
                     self.image[lb:lb + 1], grad_packed[lb:lb + 1])
 
         kind, plan = self._schedule
@@ -416,8 +469,8 @@ class ShardedFlashDeformAttnFunction(Function):
     """``apply(value, shapes, level_start_index, packed_rows, im2col_step, K, group, local_ops, part)``
 
     ``value`` is the full ``[B, N, G, D]`` on every rank; ``packed_rows`` holds this rank's rows
-    ``[b_end-b_begin, q_end-q_begin, G, L*K*4]`` of partition ``part`` (``shard_rows``); returns the matching
-    ``[.., .., G*D]`` rows of the output.  Backward returns the fully reduced ``grad_value`` (identical on
+    ``[b_end-b_begin, q_end-q_begin, G, L*K*4]`` of partition ``part`` (``shard_rows``; only the rank's heads under a
+    head split); returns the matching ``[.., .., G*D]`` rows of the output.  Backward returns the fully reduced ``grad_value`` (identical on
     every rank) and the local ``grad_packed_rows``.  ``local_ops`` is the per-rank operator
     (``CudaLocalOps()`` by default).
     """
@@ -441,7 +494,7 @@ class ShardedFlashDeformAttnFunction(Function):
         if packed_rows.shape[0] != part.b_end - part.b_begin:
             raise ValueError(f"packed_rows holds {packed_rows.shape[0]} batch element(s), the partition "
                              f"{part.b_end - part.b_begin}: slice the inputs with shard_rows()")
-        out = ops.forward(value[part.b_begin:part.b_end], shapes, lsi, packed_rows, K, im2col_step)
+        out = ops.forward(shard_value(value, part), shapes, lsi, packed_rows, K, im2col_step)
         ctx.save_for_backward(value, shapes, lsi, packed_rows)
         return out
 
@@ -456,13 +509,16 @@ class ShardedFlashDeformAttnFunction(Function):
                                              ctx.im2col_step, ctx.group, part)
             if fused is not None:
                 return (fused[0], None, None, fused[1]) + none
-        local_value = value[part.b_begin:part.b_end]
+        local_value = shard_value(value, part)
         accum, grad_packed = ctx.ops.backward_accumulate(
             local_value, shapes, lsi, packed_rows, grad_out.contiguous(), ctx.K, ctx.im2col_step)
         if ctx.multi:
-            if accum.shape[0] != value.shape[0]:  # batch-aligned partition: place the local images, sum the rest as zeros
+            if accum.shape != value.shape:  # batch-aligned partition: place the local images, sum the rest as zeros
                 full = torch.zeros(value.shape, dtype=accum.dtype, device=accum.device)
-                full[part.b_begin:part.b_end] = accum
+                if part.splits_heads:
+                    full[part.b_begin:part.b_end, :, part.h_begin:part.h_end] = accum
+                else:
+                    full[part.b_begin:part.b_end] = accum
                 accum = full
             dist.all_reduce(accum, op=dist.ReduceOp.SUM, group=ctx.group)
         return (ctx.ops.cast(accum, value.dtype), None, None, grad_packed) + none

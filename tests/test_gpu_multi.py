@@ -37,7 +37,7 @@ def _worker(rank, world, port, mode, batch, ret):
                       FDA_PEER_REDUCE_MODE=mode if mode in ("p2p", "push", "multimem") else "auto",
                       # the multicast and posted-store exchanges sum over all ranks: they need every rank on every image
                       FDA_PARTITION="queries" if mode in ("push", "multimem", "queries") else "auto")
-    if mode == "slab-pipeline":  # force the slab-binned backward and its slab-group exchange on this small problem
+    if mode in ("slab-pipeline", "heads-slabs"):  # force the slab-binned backward and its slab-group exchange on this small problem
         os.environ.update(FDA_L2_KEEP_FRACTION="0.00001", FDA_BIN_SLAB_MB="0.25", FDA_SLAB_PARTS="3")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -50,21 +50,22 @@ def _worker(rank, world, port, mode, batch, ret):
         shapes = [(8, 16, 32), (4, 8, 16)]
         K = 4
         value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, batch, 301, 8, 32, K, seed=31)
-        part = partition(batch, 301, rank, world)
+        G = 8
+        part = partition(batch, 301, rank, world, num_heads=G if mode.startswith("heads") else None)
         sh, lsi = sh.to(dev), lsi.to(dev)
         ok = True
         for step in range(2):  # twice: buffers of the first backward are reused by the second
             v = value.to(dev, torch.bfloat16).requires_grad_(True)
             pk = shard_rows(packed, part).to(dev).requires_grad_(True)
             out = sharded_flash_deform_attn(v, sh, lsi, pk, 64, K, None, None, part)
-            out.backward(shard_rows(grad_out, part).to(dev, torch.bfloat16))
+            out.backward(shard_rows(grad_out, part, G).to(dev, torch.bfloat16))
             v1 = value.to(dev, torch.bfloat16).requires_grad_(True)
             pk1 = packed.to(dev).requires_grad_(True)
             out1 = FlashDeformAttnFunction.apply(v1, sh, lsi, pk1, 64, K, True)
             out1.backward(grad_out.to(dev, torch.bfloat16))
             torch.cuda.synchronize()
             scale = v1.grad.float().abs().max().item()
-            ok &= torch.equal(out, shard_rows(out1, part))
+            ok &= torch.equal(out, shard_rows(out1, part, G))
             ok &= (v.grad.float() - v1.grad.float()).abs().max().item() <= 2e-2 * scale
             ok &= torch.equal(pk.grad, shard_rows(pk1.grad, part))
         # and against the CPU oracle, so the check does not rest on the single-GPU path alone
@@ -78,7 +79,7 @@ def _worker(rank, world, port, mode, batch, ret):
 # mode, batch size -> partition kind with two ranks
 CASES = [("p2p", 2, "batch"), ("p2p", 1, "batch-groups"), ("queries", 2, "queries"), ("push", 2, "queries"),
          ("multimem", 2, "queries"), ("nccl", 2, "batch"), ("nccl", 1, "batch-groups"), ("slab-pipeline", 2, "batch"),
-         ("slab-pipeline", 1, "batch-groups")]
+         ("slab-pipeline", 1, "batch-groups"), ("heads", 1, "batch-heads"), ("heads-slabs", 1, "batch-heads")]
 
 
 @pytest.mark.parametrize("mode,batch,kind", CASES)

@@ -70,6 +70,30 @@ def test_partition_tiles_the_rows_and_groups_share_one_batch_element(B, Q, world
         partition(B, Q, world, world)
 
 
+@pytest.mark.parametrize("B,G,world,kind,heads", [(2, 8, 8, "batch-heads", 2), (2, 8, 4, "batch-heads", 4), (1, 8, 8, "batch-heads", 1),
+                                                  (2, 8, 2, "batch", 0), (2, 6, 8, "batch-groups", 0), (1, 8, 16, "batch-groups", 0)])
+def test_head_split_is_chosen_when_the_group_size_divides_the_heads(B, G, world, kind, heads):
+    Q = 1000
+    parts = [partition(B, Q, r, world, mode="auto", num_heads=G) for r in range(world)]
+    assert all(p.kind == kind for p in parts)
+    covered = torch.zeros(B, Q, G, dtype=torch.int32)
+    for r, p in enumerate(parts):
+        h0, h1 = (p.h_begin, p.h_end) if p.splits_heads else (0, G)
+        assert (h1 - h0 == heads) if heads else not p.splits_heads
+        covered[p.b_begin:p.b_end, p.q_begin:p.q_end, h0:h1] += 1
+        assert p.group[p.group_rank] == r
+    assert bool((covered == 1).all())
+    # "rows" never splits heads; shard_rows cuts both row layouts to the rank's heads
+    assert all(not partition(B, Q, r, world, mode="rows", num_heads=G).splits_heads for r in range(world))
+    p = parts[-1]
+    if p.splits_heads:
+        t4, t3 = torch.arange(B * Q * G * 3.0).reshape(B, Q, G, 3), torch.arange(B * Q * G * 5.0).reshape(B, Q, G * 5)
+        assert torch.equal(shard_rows(t4, p), t4[p.b_begin:p.b_end, :, p.h_begin:p.h_end])
+        assert torch.equal(shard_rows(t3, p, G), t3.reshape(B, Q, G, 5)[p.b_begin:p.b_end, :, p.h_begin:p.h_end].reshape(-1, Q, heads * 5))
+        with pytest.raises(ValueError):
+            shard_rows(t3, p)
+
+
 def _worker(rank, world, port, case, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -77,14 +101,15 @@ def _worker(rank, world, port, case, ret):
         torch.set_num_threads(1)
         B, mode = case
         shapes = [(4, 6, 8), (2, 3, 4)]
-        value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, B, 13, 2, 8, 4, seed=9)
-        part = partition(B, 13, rank, world, mode=mode)
+        G = 2
+        value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, B, 13, G, 8, 4, seed=9)
+        part = partition(B, 13, rank, world, mode="auto" if mode == "heads" else mode, num_heads=G if mode == "heads" else None)
         v = value.clone().requires_grad_(True)
         pk = shard_rows(packed, part).requires_grad_(True)
         out = sharded_flash_deform_attn(v, sh, lsi, pk, 64, 4, None, OracleLocalOps(), part)
-        out.backward(shard_rows(grad_out, part))
+        out.backward(shard_rows(grad_out, part, G))
         ref_out, ref_gv, ref_gp = fda_oracle.fused_forward_backward(value, sh, packed, grad_out, 4)
-        ok = torch.allclose(out, shard_rows(ref_out, part), atol=1e-5)
+        ok = torch.allclose(out, shard_rows(ref_out, part, G), atol=1e-5)
         ok &= torch.allclose(v.grad, ref_gv, atol=1e-4)  # reduced over ranks: the full gradient on every rank
         ok &= torch.allclose(pk.grad, shard_rows(ref_gp, part), atol=1e-4)
         ret[rank] = (bool(ok), part.kind)
@@ -93,7 +118,7 @@ def _worker(rank, world, port, case, ret):
 
 
 @pytest.mark.parametrize("case,kind", [((2, "auto"), "batch"), ((1, "auto"), "batch-groups"), ((2, "queries"), "queries"),
-                                       ((3, "auto"), "queries")])
+                                       ((3, "auto"), "queries"), ((1, "heads"), "batch-heads")])
 def test_two_ranks_reproduce_the_unsharded_result(case, kind):
     world = 2
     ret = mp.get_context("spawn").Manager().dict()
