@@ -463,6 +463,8 @@ def run_ours(args, cfg):
             reducer, use_peer = None, False
             peer_note = peer_note or "peer exchange unavailable on another rank; NCCL all-reduce used"
     L = len(cfg["shapes"])
+    # which backward the library takes for this rank's rows (it works batch element by batch element under the reducer)
+    bwd_path = capi.backward_path(value_local[:1] if use_peer else value_local, packed[:1] if use_peer else packed, K)
     grad_value = accum = scratch = accum_heads = None
     if not use_peer:
         n_scratch = capi.scratch_bytes(value_local, packed, K)
@@ -650,14 +652,18 @@ def run_ours(args, cfg):
     else:
         peak, peak_src = 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
     achieved = bm["bwd_kernel"] / (bwd_ms * 1e-3) / 1e9
-    traffic, traffic_how = (measured_traffic(args.config) if (world == 1 and not args.batch and not args.queries)
+    traffic, traffic_how = (measured_traffic(args.config) if (world == 1 and not args.batch and not args.queries and not args.half_volume)
                             else (None, "captured for the full single-GPU launch only"))
     roofline = {
         "bound": "hbm",
-        "kernel": "backward pass = zero-fill + slab binning + fda_backward_binned_kernel + fda_backward_kernel (one C-ABI call)",
+        "kernel": "backward pass (one C-ABI call) = zero-fill + " + {
+            2: "cell sort (fda_sort_pass_kernel count / fill, fda_scan_*) + fda_sorted_walk_kernel + fda_sort_finalize_kernel",
+            1: "slab binning + fda_backward_binned_kernel + fda_backward_kernel",
+            0: "fda_backward_kernel"}[bwd_path],
         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
         "model": "gather model: every in-range corner row gathered (value dtype) and scattered (fp32) counts, plus the streamed "
-                 "rows; part of it is served by L2, so frac can exceed 1 -- dram_frac is the measured DRAM share",
+                 "rows; part of it is served by L2 -- and the cell-sorted backward gathers and scatters once per run of points "
+                 "in the same cell, not once per point -- so frac can exceed 1; dram_frac is the measured DRAM share",
         "traffic": traffic, "traffic_source": traffic_how,
         "dram_achieved": (traffic / (bwd_ms * 1e-3) / 1e9) if traffic else None,
         "dram_frac": (traffic / (bwd_ms * 1e-3) / 1e9 / peak) if traffic else None,
@@ -729,6 +735,9 @@ def main():
                     help="N > 1: how the fp32 grad_value images are summed (fused peer-memory kernel, or NCCL all-reduce + cast)")
     ap.add_argument("--batch", type=int, default=0, help="override B (smaller case for profiler captures)")
     ap.add_argument("--queries", type=int, default=0, help="override Lq (smaller case for profiler captures)")
+    ap.add_argument("--half-volume", action="store_true",
+                    help="halve every level extent and scale Lq with the cells (1/8 of the volume and of the rows, the same "
+                         "sampling points per cell): smaller case for profiler captures of the cell-sorted backward")
     ap.add_argument("--no-ref-cuda", action="store_true",
                     help="do not time the reference's own CUDA kernels (timed by default at N=1 when baseline/_ref/ops3d_ref_C.so exists)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
@@ -736,6 +745,12 @@ def main():
                     help="replay the step from CUDA graphs (auto: the launch-bound configurations 1-3, one GPU)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
+    if args.half_volume:
+        cells = sum(d * h * w for d, h, w in cfg["shapes"])
+        cfg["shapes"] = [tuple(max(1, v // 2) for v in shp) for shp in cfg["shapes"]]
+        small = sum(d * h * w for d, h, w in cfg["shapes"])
+        cfg["Q"] = max(1, cfg["Q"] * small // cells)
+        cfg["name"] += f" [every level extent halved, Lq={cfg['Q']}]"
     if args.batch or args.queries:
         cfg["B"] = args.batch or cfg["B"]
         cfg["Q"] = args.queries or cfg["Q"]

@@ -243,9 +243,11 @@ SortLayout sort_layout(int B, int N, int G, int D, int L, int Q, int K, int vdt)
     const unsigned long long bins = (unsigned long long)B * N * G;
     const unsigned long long points = (unsigned long long)B * Q * G * L * K;
     if (bins >= (1ull << 31) || points >= (1ull << 31)) return s;
-    // by size: a few million points at least (below that the five extra launches cost more than they save), and six
-    // points per (cell, head) on average -- the walk gathers and reduces once per RUN of equal cells, so it needs runs
-    if (g_config.sorted == 1 && (points < (4ull << 20) || (unsigned long long)Q * L * K < 6ull * N)) return s;
+    // by size: a few million points at least (below that the five extra launches cost more than they save), and ten
+    // points per (cell, head) on average -- the walk gathers and reduces once per RUN of equal cells, so it needs runs.
+    // Measured per point of one rank's rows, full-size volume: sorted 0.143 / 0.170 ns at 24 / 12 points per cell and
+    // head, the slab-binned + plain kernels 0.18 ns whatever the density; the fit a + b / density crosses at 9.5.
+    if (g_config.sorted == 1 && (points < (4ull << 20) || (unsigned long long)Q * L * K < 10ull * N)) return s;
     s.bins = bins;
     s.points = points;
     s.tiles = (unsigned int)((bins + fda::kScanTile - 1) / fda::kScanTile);

@@ -12,10 +12,10 @@ struct Config {
     int pair_rows;            // FDA_PAIR_ROWS         0 switches the paired-row scatter off (1)
     int forced_variant;       // FDA_FORCE_VARIANT     0 library's choice, 1 "reg", 2 "smem" (forward staging)
     int peer_reduce_blocks;   // FDA_PEER_REDUCE_BLOCKS  blocks of the cross-GPU exchange kernels (32)
-    int sorted;               // FDA_BWD_SORT          cell-sorted backward: 0 off, 1 when the problem is large enough, 2 always
+    int sorted;               // FDA_BWD_SORT          cell-sorted backward: 0 off, 1 for large, dense problems, 2 whenever the shape allows (1)
     int sort_seg;             // FDA_SORT_SEGMENT      list entries per lane group between flushes (32)
     int sort_grid_x;          // FDA_SORT_GRID_X       blocks per batch element walking the sorted list (0 = fill the SMs once)
-    int sort_ahead;           // FDA_SORT_AHEAD        points whose rows are in flight per lane of the walk: 2, 3 or 4 (4)
+    int sort_ahead;           // FDA_SORT_AHEAD        points whose rows are in flight per lane of the walk: 2, 3 or 4 (2)
 };
 
 const Config &config();
