@@ -182,10 +182,15 @@ int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_element
  *   last launch    flags = FDA_BWD_RESUME | FDA_BWD_FINALIZE
  * (a single launch over all levels uses FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE).  Between launches
  * grad_sampling_loc_attn holds intermediate values; it is final after the FINALIZE launch.
- * scratch (fda_backward_scratch_bytes() bytes, 256-byte aligned, may be NULL) enables the
+ * scratch (256-byte aligned, may be NULL): with fda_backward_scratch_bytes() bytes it enables the
  * slab-binned path for the largest level when it is part of the range, and keeps the logit
  * gradients handed from launch to launch in fp32 when the offsets are 16-bit (without it they pass
- * through grad_sampling_loc_attn and are rounded to 16 bits once more on the way).
+ * through grad_sampling_loc_attn and are rounded to 16 bits once more on the way); with at least
+ * fda_backward_sorted_scratch_bytes() bytes (when that is not 0) the launches take the cell-sorted
+ * path instead: the first launch of a sequence (no FDA_BWD_RESUME) sorts the points of all levels
+ * into the scratch, every launch walks its levels' part of the list, the FDA_BWD_FINALIZE launch
+ * writes grad_sampling_loc_attn (it holds nothing meaningful before).  Pass the same scratch to
+ * every launch of a sequence.
  * No counterpart in the reference.
  */
 #define FDA_BWD_ZERO_IMAGE 1

@@ -25,6 +25,22 @@ def test_peer_reduce_cast_world_of_one_is_a_cast(dtype):
     assert torch.equal(out, image.to(dtype))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_head_slice_cast_push_world_of_one_places_the_slice(dtype):
+    """The head-sharded exchange on one GPU: a compact fp32 image of heads [2, 5) lands, converted, in its place
+    inside the full gradient; cells outside the range and the other heads stay untouched."""
+    from ops3d_b200 import capi
+
+    cells, G, D, h0, h1 = 37, 8, 16, 2, 5
+    image = torch.randn(cells, h1 - h0, D, device="cuda")
+    out = torch.full((cells, G, D), 7.0, dtype=dtype, device="cuda")
+    capi.head_slice_cast_push(image.data_ptr(), [out.data_ptr()], 0, 3, 30, (h1 - h0) * D, G * D, h0 * D, dtype, image.device)
+    torch.cuda.synchronize()
+    expect = torch.full((cells, G, D), 7.0, dtype=dtype, device="cuda")
+    expect[3:33, h0:h1] = image[3:33].to(dtype)
+    assert torch.equal(out, expect)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
