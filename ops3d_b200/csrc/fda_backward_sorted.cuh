@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
     for (unsigned int sp = blockIdx.x * warps_per_block + warp; sp < nspan; sp += gridDim.x * warps_per_block) {
         const unsigned int w0 = e_begin + sp * span;
         const unsigned int wn = (e_end - w0 < span) ? e_end - w0 : span;  // entries of this warp's span
-        __syncwarp();  // the previous round's readers are done with the records
+        __syncwarp();  // the readers of the previous span are done with the records
         for (unsigned int v = lane; v < 2 * wn; v += 32) {
             const unsigned int sg = v / (2u * S);
             ent_s[sg * seg_stride + (v - sg * 2u * S)] = __ldcs(p.sort_entries + 2 * (size_t)w0 + v);
@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
-                // a group without a point this round multiplies stale rows with a zero grad_output row
+                // a group without a point in this iteration multiplies stale rows with a zero grad_output row
                 MmaDot<VT>::mma(c, va[2 * h].x, va[2 * h + 1].x, va[2 * h].y, va[2 * h + 1].y, gr.x, gr.y);
                 MmaDot<VT>::mma(c, va[2 * h].z, va[2 * h + 1].z, va[2 * h].w, va[2 * h + 1].w, gr.z, gr.w);
                 dot[2 * h] = odd ? c[1] : c[0];  // meaningful in the owner lane only
