@@ -224,13 +224,13 @@ size_t dalpha_plane_bytes(int B, int G, int L, int Q, int K, int pdt) {
     return round256((size_t)B * Q * G * L * K * sizeof(float));
 }
 
-// Cell-sorted backward: [counters [B*N*G]] [scan tile sums] [entries, 32 bytes per point] [positions, 4 bytes per
-// point] [results, 16 bytes per point].  Zero when the path is switched off or the problem does not qualify: 16-bit
+// Cell-sorted backward: [counters [B*N*G]] [scan tile sums] [entries, 32 bytes per point] [results, 16 bytes per
+// point].  Zero when the path is switched off or the problem does not qualify: 16-bit
 // values with 32 channels per head only (rows of four lanes, which is what the walk's matrix instructions assume);
 // point ids and list positions are 32-bit; FDA_BWD_SORT=1 wants at least a few million points, below that the extra
 // launches cost more than they save.
 struct SortLayout {
-    size_t counters, tile_sums, entries, positions, results, total;
+    size_t counters, tile_sums, entries, results, total;
     unsigned long long bins, points;
     unsigned int tiles;
 };
@@ -254,8 +254,7 @@ SortLayout sort_layout(int B, int N, int G, int D, int L, int Q, int K, int vdt)
     s.counters = 0;
     s.tile_sums = round256(bins * sizeof(unsigned int));
     s.entries = s.tile_sums + round256((size_t)s.tiles * sizeof(unsigned int));
-    s.positions = s.entries + round256(points * 2 * sizeof(float4));
-    s.results = s.positions + round256(points * sizeof(unsigned int));
+    s.results = s.entries + round256(points * 2 * sizeof(float4));
     s.total = s.results + round256(points * sizeof(float4));
     return s;
 }
@@ -268,7 +267,6 @@ void attach_sorted(fda::Problem &p, const Shape &s, void *scratch, size_t scratc
     p.sort_counters = reinterpret_cast<unsigned int *>(base + lay.counters);
     p.sort_tile_sums = reinterpret_cast<unsigned int *>(base + lay.tile_sums);
     p.sort_entries = reinterpret_cast<float4 *>(base + lay.entries);
-    p.sort_positions = reinterpret_cast<unsigned int *>(base + lay.positions);
     p.sort_results = reinterpret_cast<float4 *>(base + lay.results);
     p.sort_seg = g_config.sort_seg;
     p.bin_allowed = 0;  // this layout replaces the binned one

@@ -11,17 +11,18 @@
 //
 //   fda_sort_count_kernel     rows staged like in fda_backward_kernel; one counter per (batch, cell, head)
 //   fda_scan_*                exclusive scan of the counters (three small kernels, no waiting between blocks)
-//   fda_sort_fill_kernel      soft-max of the row; position = atomicAdd(counter of the point's bin); files the point
-//                             there as one 32-byte record and remembers the position per point
+//   fda_sort_pass_kernel<fill> soft-max of the row; position = atomicAdd(counter of the point's bin); files the point
+//                             there as one 32-byte record
 //   fda_sorted_walk_kernel    grid (x, batch): lane groups walk segments of the sorted list of the launch's levels.
 //                             Everything a point needs from global memory (its grad_output row, and the eight value
 //                             rows when it starts a run) is copied asynchronously into shared memory a few points
 //                             ahead.  The eight dot products <value row, grad_output row> of a point are warp-level
 //                             matrix instructions; the gradient image rows are accumulated in registers and sent with
-//                             one reduction per corner when the run ends.  Writes {d/dx, d/dy, d/dz, dalpha} at the
-//                             point's position in the list.
-//   fda_sort_finalize_kernel  per row: fetches the results of its points by position, applies the soft-max backward
-//                             and writes the finished row of grad_sampling_loc_attn, coalesced
+//                             one reduction per corner when the run ends.  Writes {d/dx, d/dy, d/dz, dalpha} of the
+//                             point into a row-ordered array (a scattered 16-byte store: the walk has DRAM bandwidth
+//                             to spare, the pass that follows would pay 64 bytes per random 16-byte read).
+//   fda_sort_finalize_kernel  per row: its points' results (contiguous), soft-max backward, finished row of
+//                             grad_sampling_loc_attn, coalesced
 //
 // A launch over a level range that is not the first of a sequence (`resume`) re-uses the list made by the first.
 // Nothing here waits on another block.  No counterpart in the reference (its backward is one thread group per query
@@ -139,9 +140,9 @@ __global__ void __launch_bounds__(kThreads) fda_sort_pass_kernel(const Problem p
                         const unsigned int meta = (unsigned int)l | (g << 4) | (tag.in8 << 20);
                         float4 *rec = p.sort_entries + 2 * (size_t)pos[u];
                         __stcs(rec, make_float4(xv, yv, zv, __expf(trow[3 * LK + i] - m) * inv));
-                        __stcs(rec + 1, make_float4(__uint_as_float((unsigned int)rowg), __uint_as_float(meta), __uint_as_float(tag.off0), 0.f));
+                        __stcs(rec + 1, make_float4(__uint_as_float((unsigned int)rowg), __uint_as_float(meta), __uint_as_float(tag.off0),
+                                                    __uint_as_float((unsigned int)i)));
                     }
-                    p.sort_positions[rowg * (size_t)LK + i] = pos[u];
                 }
             }
         }
@@ -376,7 +377,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
             float4 ent = make_float4(0.f, 0.f, 0.f, 0.f), tag = ent;
             if (have) {
                 ent = ent_g[2 * t];       // voxel x, y, z, probability
-                tag = ent_g[2 * t + 1];   // row, level | head << 4 | corner mask << 20, base offset
+                tag = ent_g[2 * t + 1];   // row, level | head << 4 | corner mask << 20, base offset, point index inside the row
             }
             const unsigned int meta = __float_as_uint(tag.y), off0 = __float_as_uint(tag.z);
             cp_async_wait<kAhead - 1>();
@@ -421,7 +422,8 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
                 float da = 0.f;
 #pragma unroll
                 for (int n = 0; n < 8; ++n) da = fmaf((wx[n & 1] * wy[(n >> 1) & 1]) * wz[n >> 2], dot[n], da);
-                __stcs(p.sort_results + (size_t)w0 + t0 + t, make_float4(a * lv.fW * gx, a * lv.fH * gy, a * lv.fD * gz, da));
+                __stcs(p.sort_results + (size_t)__float_as_uint(tag.x) * (size_t)p.LK + __float_as_uint(tag.w),
+                       make_float4(a * lv.fW * gx, a * lv.fH * gy, a * lv.fD * gz, da));
             }
             float god[8];
             Vec16<VT>::unpack(gr, god);
@@ -440,11 +442,14 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
     }
 }
 
-// Per row: results of its points (by position), soft-max backward, finished row of grad_sampling_loc_attn.
+// Per row: the results of its points, soft-max backward, finished row of grad_sampling_loc_attn.  A point without a
+// corner inside its level was never filed and has no result: its gradients are zero (the same test as in the fill pass).
 template <typename PT>
 __global__ void __launch_bounds__(kThreads) fda_sort_finalize_kernel(const Problem p) {
+    __shared__ LevelGeom geom[kMaxLevels];
     extern __shared__ __align__(16) float smem_tile[];
     const int tid = threadIdx.x;
+    if (tid == 0) build_level_table(geom, p.shapes, p.lsi, p.L, p.GD, p.value_elem_bytes, false, 0ull);
     const int b = blockIdx.y;
     const int gs = 1 << p.gs_log2;
     const int lane = tid & 31, warp = tid >> 5;
@@ -458,38 +463,43 @@ __global__ void __launch_bounds__(kThreads) fda_sort_finalize_kernel(const Probl
     float *wtile = smem_tile + warp * rows_per_warp * p.row_stride;
     int nrows = p.rows_per_b - first;
     nrows = nrows < 0 ? 0 : (nrows > rows_per_warp ? rows_per_warp : nrows);
+    const size_t warp_elem0 = ((size_t)b * p.rows_per_b + first) * (size_t)(4 * LK);
+    stage_rows<PT>(static_cast<const PT *>(p.packed) + warp_elem0, wtile, nrows, LK, p.row_stride, lane);
+    __syncthreads();  // level table and this warp's tile visible
     float *trow = wtile + (lane >> p.gs_log2) * p.row_stride;
     const size_t rowg = (size_t)b * p.rows_per_b + (row_ok ? row : 0);
-    const PT *logits = static_cast<const PT *>(p.packed) + rowg * (size_t)(4 * LK) + 3 * LK;
-    const unsigned int *pos = p.sort_positions + rowg * (size_t)LK;
+    const unsigned int g = row_ok ? (unsigned int)(row % p.G) : 0u;
+    const float4 *results = p.sort_results + rowg * (size_t)LK;
     const int rounds = (LK + gs - 1) >> p.gs_log2;  // uniform over the warp
 
+    // Tile row layout: [0,3LK) coordinates -> coordinate gradients, [3LK,4LK) logits -> dalpha -> logit gradients,
+    // [4LK,5LK) exp(logit - max).
     float m = -INFINITY;
     for (int j = 0; j < rounds; ++j) {
         const int i = lane_c + j * gs;
-        if (row_ok && i < LK) m = fmaxf(m, load1<PT>(logits + i));
+        if (row_ok && i < LK) m = fmaxf(m, trow[3 * LK + i]);
     }
     for (int mask = gs >> 1; mask > 0; mask >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, mask));
     float s = 0.f, S = 0.f;
-    constexpr int kBatch = 8;  // positions of eight points first, then their eight results, then the arithmetic
+    constexpr int kBatch = 8;  // the results of eight points are requested before the first one is used
     for (int j0 = 0; j0 < rounds; j0 += kBatch) {
-        unsigned int at[kBatch];
         float4 r[kBatch];
 #pragma unroll
         for (int j = 0; j < kBatch; ++j) {
             const int i = lane_c + (j0 + j) * gs;
-            at[j] = (row_ok && i < LK) ? __ldcs(pos + i) : kNoPosition;
-        }
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
             r[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (at[j] != kNoPosition) r[j] = __ldcs(p.sort_results + at[j]);
+            if (row_ok && i < LK) {
+                const LevelGeom lv = geom[(i >> 2) >> p.k_shift];
+                const SortTag tag = sort_tag_of(lv, p.G, p.GD, g, unnormalize(trow[3 * i], lv.fW), unnormalize(trow[3 * i + 1], lv.fH),
+                                                unnormalize(trow[3 * i + 2], lv.fD));
+                if (tag.ok) r[j] = __ldcs(results + i);
+            }
         }
 #pragma unroll
         for (int j = 0; j < kBatch; ++j) {
             const int i = lane_c + (j0 + j) * gs;
             if (row_ok && i < LK) {
-                const float ex = __expf(load1<PT>(logits + i) - m);
+                const float ex = __expf(trow[3 * LK + i] - m);
                 trow[3 * i] = r[j].x; trow[3 * i + 1] = r[j].y; trow[3 * i + 2] = r[j].z;
                 trow[3 * LK + i] = r[j].w;   // dalpha
                 trow[4 * LK + i] = ex;
@@ -509,7 +519,7 @@ __global__ void __launch_bounds__(kThreads) fda_sort_finalize_kernel(const Probl
         if (row_ok && i < LK) trow[3 * LK + i] = trow[4 * LK + i] * inv * (trow[3 * LK + i] - S);
     }
     __syncwarp();
-    PT *dst = static_cast<PT *>(p.grad_packed) + ((size_t)b * p.rows_per_b + first) * (size_t)(4 * LK);
+    PT *dst = static_cast<PT *>(p.grad_packed) + warp_elem0;
     const int nvec = nrows * LK;
     const float inv_lk = 1.0f / (float)LK;
     for (int v = lane; v < nvec; v += 32) {

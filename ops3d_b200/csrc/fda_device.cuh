@@ -74,9 +74,8 @@ struct Problem {
     unsigned int *sort_tile_sums;  // scratch of the scan
     float4 *sort_entries;          // sorted list, 32 bytes per point: {voxel x, y, z inside the point's level, soft-max
                                    // probability} {row b*Q*G + q*G + g, level | head << 4 | corner mask << 20, element
-                                   // offset of the base corner, 0}
-    unsigned int *sort_positions;  // [B*Q*G*L*K]: position of every point in the list (kNoPosition: no corner in range)
-    float4 *sort_results;          // per list position: {d/dx, d/dy, d/dz, dalpha}
+                                   // offset of the base corner, index of the point inside its row}
+    float4 *sort_results;          // [B*Q*G][L*K] in row order: {d/dx, d/dy, d/dz, dalpha} of every filed point
     int sort_seg;                  // list entries one lane group walks before it flushes its accumulators
 };
 
