@@ -60,6 +60,7 @@ fda::Config read_config() {
     c.pair_rows = 1;
     c.forced_variant = 0;
     c.peer_reduce_blocks = 32;
+    c.fwd_head_groups = 1;
     c.sorted = 1;
     c.sort_seg = 32;
     c.sort_grid_x = 0;
@@ -77,6 +78,7 @@ fda::Config read_config() {
     }
     if (const char *e = std::getenv("FDA_PEER_REDUCE_BLOCKS")) c.peer_reduce_blocks = std::atoi(e);
     if (c.peer_reduce_blocks < 1) c.peer_reduce_blocks = 1;
+    if (const char *e = std::getenv("FDA_FWD_HEAD_GROUPS")) c.fwd_head_groups = std::atoi(e);
     if (const char *e = std::getenv("FDA_BWD_SORT")) c.sorted = std::atoi(e);
     if (const char *e = std::getenv("FDA_SORT_SEGMENT")) c.sort_seg = std::atoi(e);
     c.sort_seg = (c.sort_seg + 3) & ~3;
@@ -142,6 +144,7 @@ fda::Problem make_problem(const Shape &s) {
     p.GD = s.G * s.D;
     p.value_elem_bytes = dtype_size(s.vdt);
     p.l2_keep_bytes = l2_keep_budget();
+    p.head_group = s.G;
     p.level_mask = (1 << s.L) - 1;
     p.finalize = 1;
     p.slab_part = 0;
@@ -187,17 +190,36 @@ inline dim3 row_grid(const fda::Problem &p, int threads) {
     return dim3((unsigned)((p.rows_per_b + rows_per_block - 1) / rows_per_block), (unsigned)p.B, 1);
 }
 
+// Heads per group of the forward's row order: when one batch element's value volume exceeds the L2 budget and the call
+// is large, the largest power-of-two divisor of G whose share of the volume fits; G (plain row order) otherwise.
+int forward_head_group(const fda::Problem &p) {
+    if (g_config.fwd_head_groups == 0) return p.G;
+    const unsigned long long volume = (unsigned long long)p.N * p.GD * p.value_elem_bytes;
+    if (g_config.fwd_head_groups == 1 && (volume <= p.l2_keep_bytes || (unsigned long long)p.rows_per_b * p.LK < (4ull << 20))) return p.G;
+    int hg = p.G;
+    while (hg > 1 && hg % 2 == 0 && volume / p.G * hg > p.l2_keep_bytes) hg /= 2;
+    return hg;
+}
+
+// grid of a forward launch: blocks per head group x groups, batch elements
+inline dim3 forward_grid(const fda::Problem &p, int threads) {
+    const int rows_per_block = threads >> p.gs_log2;
+    const int rows_per_group = p.Q * p.head_group;
+    return dim3((unsigned)(((rows_per_group + rows_per_block - 1) / rows_per_block) * (p.G / p.head_group)), (unsigned)p.B, 1);
+}
+
 template <typename VT, typename PT>
 int launch_forward(fda::Problem p, bool stage, cudaStream_t st) {
+    p.head_group = forward_head_group(p);
     if (stage) {
         p.row_stride = padded_stride(4 * p.LK);
         const int threads = pick_threads(p, p.row_stride);
         const size_t smem = (size_t)(threads >> p.gs_log2) * p.row_stride * sizeof(float);
         auto kern = fda::fda_forward_kernel<VT, PT, true>;
         if (int rc = ensure_smem(reinterpret_cast<const void *>(kern), smem)) return rc;
-        kern<<<row_grid(p, threads), threads, smem, st>>>(p);
+        kern<<<forward_grid(p, threads), threads, smem, st>>>(p);
     } else {
-        fda::fda_forward_kernel<VT, PT, false><<<row_grid(p, fda::kThreads), fda::kThreads, 0, st>>>(p);
+        fda::fda_forward_kernel<VT, PT, false><<<forward_grid(p, fda::kThreads), fda::kThreads, 0, st>>>(p);
     }
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FDA_OK : cuda_fail(e);

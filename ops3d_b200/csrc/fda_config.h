@@ -12,6 +12,7 @@ struct Config {
     int pair_rows;            // FDA_PAIR_ROWS         0 switches the paired-row scatter off (1)
     int forced_variant;       // FDA_FORCE_VARIANT     0 library's choice, 1 "reg", 2 "smem" (forward staging)
     int peer_reduce_blocks;   // FDA_PEER_REDUCE_BLOCKS  blocks of the cross-GPU exchange kernels (32)
+    int fwd_head_groups;      // FDA_FWD_HEAD_GROUPS   forward walks the rows head group by head group: 0 never, 1 for large calls whose value volume exceeds L2, 2 whenever the volume exceeds the budget (1)
     int sorted;               // FDA_BWD_SORT          cell-sorted backward: 0 off, 1 for large, dense problems, 2 whenever the shape allows (1)
     int sort_seg;             // FDA_SORT_SEGMENT      list entries per lane group between flushes (32)
     int sort_grid_x;          // FDA_SORT_GRID_X       blocks per batch element walking the sorted list (0 = fill the SMs once)

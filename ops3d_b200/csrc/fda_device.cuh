@@ -52,6 +52,7 @@ struct Problem {
     int rows_per_b;  // Q * G
     int GD;          // G * D
     int row_stride;  // floats per staged row in shared memory
+    int head_group;  // forward: heads per group of the group-by-group row order (G: plain row order)
     unsigned long long l2_keep_bytes;  // how much per-batch-element data may be marked "evict last" in L2
     int value_elem_bytes;              // sizeof(value dtype)
     // backward only

@@ -13,6 +13,11 @@
 // gather with one predicated 16-byte load per corner and lane, fp32 accumulation, and
 // one 16-byte store of the finished channels.  No thread block barrier besides the one
 // that publishes the level table; warps never wait on each other.
+//
+// Head groups (p.head_group = heads per group, a divisor of G): the grid walks the rows group by group -- all queries
+// for heads [0, hg), then all queries for heads [hg, 2 hg), ... -- instead of query by query, so that at any time the
+// gathers touch only hg / G of the value volume.  With a volume larger than L2 (config 5: 306 MB per batch element)
+// and points spread all over it, a group of two heads (77 MB) stays L2-resident where the whole volume does not.
 #pragma once
 
 #include "fda_device.cuh"
@@ -37,22 +42,40 @@ __global__ void __launch_bounds__(kThreads, FDA_FWD_MIN_BLOCKS) fda_forward_kern
     const int gs = 1 << p.gs_log2;
     const int lane_c = tid & (gs - 1);
     const int rows_per_block = (int)blockDim.x >> p.gs_log2;
-    const int row = blockIdx.x * rows_per_block + (tid >> p.gs_log2);  // q * G + g inside batch element b
-    const bool row_ok = row < p.rows_per_b;
+    // position of the row in head-group order -> (query, head); with head_group == G this is the identity
+    const int hg = p.head_group, rows_per_group = p.Q * hg;
+    const int blocks_per_group = (rows_per_group + rows_per_block - 1) / rows_per_block;
+    const int group = blockIdx.x / blocks_per_group;
+    const int local0 = (blockIdx.x - group * blocks_per_group) * rows_per_block;
+    auto row_at = [&](int local) -> int { const int q = local / hg; return q * p.G + group * hg + (local - q * hg); };
+    const int local = local0 + (tid >> p.gs_log2);
+    const bool row_ok = local < rows_per_group;
+    const int row = row_ok ? row_at(local) : 0;  // q * G + g inside batch element b
     const bool active = row_ok && lane_c < p.lpg;
     const int LK = p.LK;
 
-    const PT *packed_row = static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + (row_ok ? row : 0)) * (size_t)(4 * LK);
+    const PT *packed_row = static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + row) * (size_t)(4 * LK);
     const float *tile_row = nullptr;
     if (kStage) {
         const int warp = tid >> 5, lane = tid & 31;
         const int rows_per_warp = 32 >> p.gs_log2;
-        const int first = blockIdx.x * rows_per_block + warp * rows_per_warp;
+        const int first = local0 + warp * rows_per_warp;
         float *wtile = smem_tile + warp * rows_per_warp * p.row_stride;
-        int nrows = p.rows_per_b - first;
+        int nrows = rows_per_group - first;
         nrows = nrows < 0 ? 0 : (nrows > rows_per_warp ? rows_per_warp : nrows);
-        stage_rows<PT>(static_cast<const PT *>(p.packed) + ((size_t)b * p.rows_per_b + first) * (size_t)(4 * LK),
-                       wtile, nrows, LK, p.row_stride, lane);
+        const PT *packed_b = static_cast<const PT *>(p.packed) + (size_t)b * p.rows_per_b * (size_t)(4 * LK);
+        if (hg == p.G) {  // the warp's rows are one contiguous span
+            stage_rows<PT>(packed_b + (size_t)first * (size_t)(4 * LK), wtile, nrows, LK, p.row_stride, lane);
+        } else {          // hg consecutive rows per query
+            const int nvec = nrows * LK;
+            const float inv_lk = 1.0f / (float)LK;
+            for (int v = lane; v < nvec; v += 32) {
+                const int r = row_of_vector(v, inv_lk);
+                const int c = (v - r * LK) * 4;
+                *reinterpret_cast<float4 *>(wtile + r * p.row_stride + c) =
+                    load4_stream<PT>(packed_b + (size_t)row_at(first + r) * (size_t)(4 * LK) + c);
+            }
+        }
         tile_row = wtile + ((tid & 31) >> p.gs_log2) * p.row_stride;
     }
     __syncthreads();  // level table (and, when staging, this warp's tile) visible
@@ -78,7 +101,7 @@ __global__ void __launch_bounds__(kThreads, FDA_FWD_MIN_BLOCKS) fda_forward_kern
     }
     const float inv = 1.0f / s;
 
-    const int g = row_ok ? row % p.G : 0;
+    const int g = row % p.G;
     const VT *value_b = static_cast<const VT *>(p.value) + (size_t)b * p.N * p.GD + (size_t)g * p.D + (size_t)lane_c * CPL;
 
     float acc[CPL];
