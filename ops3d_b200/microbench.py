@@ -201,9 +201,22 @@ def bench_exchange(args, dev, rank, world):
             "nvlink_out_GBs": pushed / ms / 1e6, "blocks": int(os.environ.get("FDA_PEER_REDUCE_BLOCKS", "32"))}
 
 
+def bench_headpush(args, dev):
+    """The head-sharded exchange in a world of one: a compact fp32 image of 2 of 8 heads, converted and stored into its
+    place inside the full bf16 gradient (the kernel's stores are then all local)."""
+    G, D, gr = 8, 32, 2
+    cells = int(args.mb * 1e6 / 4) // (gr * D)
+    image = torch.randn(cells, gr, D, device=dev)
+    out = torch.zeros(cells, G, D, dtype=torch.bfloat16, device=dev)
+    ms = _time(lambda: capi.head_slice_cast_push(image.data_ptr(), [out.data_ptr()], 0, 0, cells, gr * D, G * D, 3 * gr * D,
+                                                 torch.bfloat16, dev), args.steps, args.warmup)
+    n = image.numel()
+    return {"kernel": "fda_head_slice_push_kernel<bf16, world 1>", "elements": n, "ms": ms, "bytes": n * 6, "GBs": n * 6 / ms / 1e6}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["cast", "pack", "prepass", "project", "dcnv4", "exchange"])
+    ap.add_argument("what", choices=["cast", "pack", "prepass", "project", "dcnv4", "exchange", "headpush"])
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--mb", type=float, default=256.0, help="fp32 image size in MB (cast, exchange)")
@@ -228,6 +241,8 @@ def main():
         res = bench_project(args, dev)
     elif args.what == "dcnv4":
         res = bench_dcnv4(args, dev)
+    elif args.what == "headpush":
+        res = bench_headpush(args, dev)
     else:
         res = bench_exchange(args, dev, rank, world)
     if rank == 0:
