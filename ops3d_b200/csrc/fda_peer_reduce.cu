@@ -397,14 +397,29 @@ template <typename VT>
 __global__ void __launch_bounds__(512) fda_head_slice_push_kernel(const float *__restrict__ image, const PeerPtrs pp, const int n_out,
                                                                   size_t unit_begin, size_t unit_end, unsigned int slice_units,
                                                                   unsigned int full_units, unsigned int head_units) {
+    constexpr int kUnroll = 4;  // units per thread and iteration, a grid stride apart: all loads go out before the first store
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t u = unit_begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < unit_end; u += stride) {
-        const float4 *src = reinterpret_cast<const float4 *>(image + u * 8);
-        const float4 lo = __ldcs(src), hi = __ldcs(src + 1);
-        const float a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        const size_t cell = u / slice_units;
-        const size_t dst = cell * full_units + head_units + (u - cell * slice_units);  // 8-element unit inside the full tensor
-        for (int p = 0; p < n_out; ++p) Out8<VT>::store(pp.out[p], dst, a);
+    for (size_t u0 = unit_begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x; u0 < unit_end; u0 += stride * kUnroll) {
+        float4 lo[kUnroll], hi[kUnroll];
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const size_t u = u0 + (size_t)j * stride;
+            if (u < unit_end) {
+                const float4 *src = reinterpret_cast<const float4 *>(image + u * 8);
+                lo[j] = __ldcs(src);
+                hi[j] = __ldcs(src + 1);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const size_t u = u0 + (size_t)j * stride;
+            if (u < unit_end) {
+                const float a[8] = {lo[j].x, lo[j].y, lo[j].z, lo[j].w, hi[j].x, hi[j].y, hi[j].z, hi[j].w};
+                const size_t cell = u / slice_units;
+                const size_t dst = cell * full_units + head_units + (u - cell * slice_units);  // 8-element unit inside the full tensor
+                for (int p = 0; p < n_out; ++p) Out8<VT>::store(pp.out[p], dst, a);
+            }
+        }
     }
 }
 
