@@ -92,6 +92,29 @@ def test_level_range_and_slab_part_validation():
     assert lib.fda_backward_accumulate_levels(p, p, p, p, p, p, p, *dims, 0, 2, 2 | 4 | 8, None, 0, None) == 8
 
 
+def test_cell_sorted_path_selection_and_scratch_size():
+    """Which backward a problem takes, and what the cell-sorted one needs: pure host functions of the shape."""
+    lib = capi.load()
+    B, N, G, D, L, Q, K = 2, 598016, 8, 32, 3, 598016, 8
+    points, bins = B * Q * G * L * K, B * N * G
+    r256 = lambda n: (n + 255) // 256 * 256  # noqa: E731
+    tiles = (bins + 8191) // 8192
+    want = r256(bins * 4) + r256(tiles * 4) + r256(points * 32) + r256(points * 16)
+    assert lib.fda_backward_sorted_scratch_bytes(B, N, G, D, L, Q, K, 2) == want     # bf16: counters, scan, records, results
+    assert lib.fda_backward_sorted_scratch_bytes(B, N, G, D, L, Q, K, 1) == want     # fp16 too
+    assert lib.fda_backward_path(B, N, G, D, L, Q, K, 2) == 2
+    assert lib.fda_backward_workspace_bytes(B, N, G, D, L, Q, K, 2, 0) == B * N * G * D * 4 + want
+    assert lib.fda_backward_sorted_scratch_bytes(B, N, G, D, L, Q, K, 0) == 0        # fp32 values: not this path
+    assert lib.fda_backward_path(B, N, G, D, L, Q, K, 0) == 1                        # ... but the image exceeds L2: brick-binned
+    assert lib.fda_backward_sorted_scratch_bytes(B, N, G, 64, L, Q, K, 2) == 0       # 64 channels per head: not this path
+    assert lib.fda_backward_sorted_scratch_bytes(B, N, G, D, L, Q // 16, K, 2) == 0  # 1.5 points per cell and head: too sparse
+    assert lib.fda_backward_path(B, N, G, D, L, Q // 16, K, 2) == 1
+    assert lib.fda_backward_sorted_scratch_bytes(1, 288, 4, 32, 2, 288, 4, 2) == 0   # a few thousand points: too small
+    assert lib.fda_backward_path(1, 288, 4, 32, 2, 288, 4, 2) == 0
+    # one rank of a head-split job at 8 GPUs: one batch element, 2 heads, every query -- as dense as the whole problem
+    assert lib.fda_backward_path(1, N, 2, D, L, Q, K, 2) == 2
+
+
 def test_exchange_kernels_validate_before_launch():
     lib = capi.load()
     ptrs = (ctypes.c_void_p * 2)(256, 512)
@@ -103,6 +126,12 @@ def test_exchange_kernels_validate_before_launch():
     assert lib.fda_peer_reduce_cast(bad, ptrs, 2, 0, 64, 2, None) == 9       # misaligned peer buffer
     assert lib.fda_multimem_reduce_cast(None, ctypes.c_void_p(256), 2, 0, 64, 2, None) == 1
     assert lib.fda_peer_push_partials(ctypes.c_void_p(256), ptrs, 16, 2, 0, 64, None) == 6  # slot shorter than a slice
+    img = ctypes.c_void_p(256)
+    assert lib.fda_head_slice_cast_push(None, ptrs, 2, 0, 0, 10, 64, 256, 64, 2, None) == 1
+    assert lib.fda_head_slice_cast_push(img, ptrs, 2, 0, 0, 10, 64, 256, 224, 2, None) == 6   # slice does not fit behind the offset
+    assert lib.fda_head_slice_cast_push(img, ptrs, 2, 0, 0, 10, 60, 256, 64, 2, None) == 6    # not a multiple of 8 elements
+    assert lib.fda_head_slice_cast_push(img, bad, 2, 0, 0, 10, 64, 256, 64, 2, None) == 9     # misaligned peer buffer
+    assert lib.fda_head_slice_cast_push(img, ptrs, 2, 0, 0, 0, 64, 256, 64, 2, None) == 0     # nothing to do: no launch
     assert lib.fda_pack_sampling(None, None, None, None, None, 1, 1, 1, 1, 4, 0, None) == 1
     assert lib.fda_pack_sampling(ctypes.c_void_p(256), ctypes.c_void_p(256), ctypes.c_void_p(256), ctypes.c_void_p(256),
                                  ctypes.c_void_p(256), 1, 1, 1, 6, 4, 0, None) == 3
