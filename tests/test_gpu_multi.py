@@ -49,7 +49,7 @@ def _free_port():
 
 def _worker(rank, world, port, mode, batch, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
-                      FDA_SHARDED_REDUCE="nccl" if mode == "nccl" else "peer",
+                      FDA_SHARDED_REDUCE="nccl" if mode in ("nccl", "heads-nccl") else "peer",
                       FDA_PEER_REDUCE_MODE=mode if mode in ("p2p", "push", "multimem") else "auto",
                       # the multicast and posted-store exchanges sum over all ranks: they need every rank on every image
                       FDA_PARTITION="queries" if mode in ("push", "multimem", "queries") else "auto")
@@ -95,7 +95,7 @@ def _worker(rank, world, port, mode, batch, ret):
 # mode, batch size -> partition kind with two ranks
 CASES = [("p2p", 2, "batch"), ("p2p", 1, "batch-groups"), ("queries", 2, "queries"), ("push", 2, "queries"),
          ("multimem", 2, "queries"), ("nccl", 2, "batch"), ("nccl", 1, "batch-groups"), ("slab-pipeline", 2, "batch"),
-         ("slab-pipeline", 1, "batch-groups"), ("heads", 1, "batch-heads"), ("heads-slabs", 1, "batch-heads")]
+         ("slab-pipeline", 1, "batch-groups"), ("heads", 1, "batch-heads"), ("heads-slabs", 1, "batch-heads"), ("heads-nccl", 1, "batch-heads")]
 
 
 @pytest.mark.parametrize("mode,batch,kind", CASES)
