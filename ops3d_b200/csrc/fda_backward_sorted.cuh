@@ -64,6 +64,12 @@ __device__ __forceinline__ SortTag sort_tag_of(const LevelGeom &lv, int G, int G
     return t;
 }
 
+// One 32-byte list record as ONE streaming store (sm_100: 256-bit vector store); `rec` is 32-byte aligned.
+__device__ __forceinline__ void store_record(float4 *rec, const float4 &a, const float4 &b) {
+    asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(rec), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w),
+                 "f"(b.x), "f"(b.y), "f"(b.z), "f"(b.w) : "memory");
+}
+
 // kFill = false: counts the points of every bin.  kFill = true: the counters hold the exclusive scan; files the points.
 template <typename PT, bool kFill>
 __global__ void __launch_bounds__(kThreads) fda_sort_pass_kernel(const Problem p) {
@@ -138,10 +144,9 @@ __global__ void __launch_bounds__(kThreads) fda_sort_pass_kernel(const Problem p
                         const SortTag tag = sort_tag_of(lv, p.G, p.GD, g, xv, yv, zv);
                         // one 32-byte record = one whole sector (no read-modify-write behind the store)
                         const unsigned int meta = (unsigned int)l | (g << 4) | (tag.in8 << 20);
-                        float4 *rec = p.sort_entries + 2 * (size_t)pos[u];
-                        __stcs(rec, make_float4(xv, yv, zv, __expf(trow[3 * LK + i] - m) * inv));
-                        __stcs(rec + 1, make_float4(__uint_as_float((unsigned int)rowg), __uint_as_float(meta), __uint_as_float(tag.off0),
-                                                    __uint_as_float((unsigned int)i)));
+                        store_record(p.sort_entries + 2 * (size_t)pos[u], make_float4(xv, yv, zv, __expf(trow[3 * LK + i] - m) * inv),
+                                     make_float4(__uint_as_float((unsigned int)rowg), __uint_as_float(meta), __uint_as_float(tag.off0),
+                                                 __uint_as_float((unsigned int)i)));
                     }
                 }
             }
