@@ -9,10 +9,10 @@
 // pyramid with K = 8 points per level and one query per cell), and the plain and the slab-binned kernels are bound by
 // exactly those gathers and reductions (the request path from the SMs to L2), not by HBM.
 //
-//   fda_sort_count_kernel     rows staged like in fda_backward_kernel; one counter per (batch, cell, head)
+//   fda_sort_pass_kernel<count> rows staged like in fda_backward_kernel; one counter per (batch, cell, head)
 //   fda_scan_*                exclusive scan of the counters (three small kernels, no waiting between blocks)
 //   fda_sort_pass_kernel<fill> soft-max of the row; position = atomicAdd(counter of the point's bin); files the point
-//                             there as one 32-byte record
+//                             there as one 32-byte record (one 256-bit store)
 //   fda_sorted_walk_kernel    grid (x, batch): lane groups walk segments of the sorted list of the launch's levels.
 //                             Everything a point needs from global memory (its grad_output row, and the eight value
 //                             rows when it starts a run) is copied asynchronously into shared memory a few points
@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
     const bool odd = grp & 1;
     const unsigned int warps_per_block = blockDim.x >> 5;
     const unsigned int S = (unsigned int)p.sort_seg;
-    const unsigned int span = S * 8u;  // list entries of one warp and round
+    const unsigned int span = S * 8u;  // list entries a warp takes at a time
     const unsigned int nspan = (e_end - e_begin + span - 1) / span;
     const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
     const VT *go_base = static_cast<const VT *>(p.grad_out) + (size_t)tig * 8;
