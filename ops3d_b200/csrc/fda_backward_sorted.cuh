@@ -242,19 +242,22 @@ template <int kPending> __device__ __forceinline__ void cp_async_wait() {
 // vectors of the grad_output row), so D[g][g] of an m16n8k16 product is the dot product over 16 channels, summed over
 // the group's lanes.  Two corners ride in one instruction (fragment rows g and g + 8), two instructions cover the 32
 // channels.  The other 7/8 of each product (row g against the grad_output of the other groups) is discarded.
+// `first`: d = A * B (zero accumulator input); `mma`: c += A * B.
+#define FDA_MMA_DOT(TYPES)                                                                                                             \
+    static __device__ __forceinline__ void first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,      \
+                                                 uint32_t b1) {                                                                         \
+        asm("mma.sync.aligned.m16n8k16.row.col." TYPES " {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"           \
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));       \
+    }                                                                                                                                   \
+    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,        \
+                                               uint32_t b1) {                                                                           \
+        asm("mma.sync.aligned.m16n8k16.row.col." TYPES " {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"               \
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));                 \
+    }
 template <typename VT> struct MmaDot;
-template <> struct MmaDot<__nv_bfloat16> {
-    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    }
-};
-template <> struct MmaDot<__half> {
-    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    }
-};
+template <> struct MmaDot<__nv_bfloat16> { FDA_MMA_DOT("f32.bf16.bf16.f32") };
+template <> struct MmaDot<__half> { FDA_MMA_DOT("f32.f16.f16.f32") };
+#undef FDA_MMA_DOT
 
 // Work unit: a segment of S consecutive list entries per lane group; the groups of a warp take consecutive segments, so a
 // warp's share of one round is one contiguous span of the list, which it first copies to shared memory (coalesced).
@@ -409,24 +412,29 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
             float dot[8];
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                float c[4];
                 // a group without a point in this iteration multiplies stale rows with a zero grad_output row
-                MmaDot<VT>::mma(c, va[2 * h].x, va[2 * h + 1].x, va[2 * h].y, va[2 * h + 1].y, gr.x, gr.y);
+                MmaDot<VT>::first(c, va[2 * h].x, va[2 * h + 1].x, va[2 * h].y, va[2 * h + 1].y, gr.x, gr.y);
                 MmaDot<VT>::mma(c, va[2 * h].z, va[2 * h + 1].z, va[2 * h].w, va[2 * h + 1].w, gr.z, gr.w);
                 dot[2 * h] = odd ? c[1] : c[0];  // meaningful in the owner lane only
                 dot[2 * h + 1] = odd ? c[3] : c[2];
             }
+            // Every lane does the owner's arithmetic (the warp pays for it either way): the corner weights are then
+            // shared between the point's own gradients and its contribution to the image rows.
+            const float wyx[4] = {wy[0] * wx[0], wy[0] * wx[1], wy[1] * wx[0], wy[1] * wx[1]};
+            const float wzy[4] = {wz[0] * wy[0], wz[0] * wy[1], wz[1] * wy[0], wz[1] * wy[1]};
+            const float wzx[4] = {wz[0] * wx[0], wz[0] * wx[1], wz[1] * wx[0], wz[1] * wx[1]};
+            float w[8];  // corner n = dz*4 + dy*2 + dx
+#pragma unroll
+            for (int n = 0; n < 8; ++n) w[n] = wyx[n & 3] * wz[n >> 2];
+            const float gx = wzy[0] * (dot[1] - dot[0]) + wzy[1] * (dot[3] - dot[2]) + wzy[2] * (dot[5] - dot[4]) + wzy[3] * (dot[7] - dot[6]);
+            const float gy = wzx[0] * (dot[2] - dot[0]) + wzx[1] * (dot[3] - dot[1]) + wzx[2] * (dot[6] - dot[4]) + wzx[3] * (dot[7] - dot[5]);
+            const float gz = wyx[0] * (dot[4] - dot[0]) + wyx[1] * (dot[5] - dot[1]) + wyx[2] * (dot[6] - dot[2]) + wyx[3] * (dot[7] - dot[3]);
+            float da = 0.f;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) da = fmaf(w[n], dot[n], da);
             if (have && tig == owner) {
                 const LevelGeom lv = geom[meta & 15u];
-                const float wzy[4] = {wz[0] * wy[0], wz[0] * wy[1], wz[1] * wy[0], wz[1] * wy[1]};
-                const float wzx[4] = {wz[0] * wx[0], wz[0] * wx[1], wz[1] * wx[0], wz[1] * wx[1]};
-                const float wyx[4] = {wy[0] * wx[0], wy[0] * wx[1], wy[1] * wx[0], wy[1] * wx[1]};
-                const float gx = wzy[0] * (dot[1] - dot[0]) + wzy[1] * (dot[3] - dot[2]) + wzy[2] * (dot[5] - dot[4]) + wzy[3] * (dot[7] - dot[6]);
-                const float gy = wzx[0] * (dot[2] - dot[0]) + wzx[1] * (dot[3] - dot[1]) + wzx[2] * (dot[6] - dot[4]) + wzx[3] * (dot[7] - dot[5]);
-                const float gz = wyx[0] * (dot[4] - dot[0]) + wyx[1] * (dot[5] - dot[1]) + wyx[2] * (dot[6] - dot[2]) + wyx[3] * (dot[7] - dot[3]);
-                float da = 0.f;
-#pragma unroll
-                for (int n = 0; n < 8; ++n) da = fmaf((wx[n & 1] * wy[(n >> 1) & 1]) * wz[n >> 2], dot[n], da);
                 __stcs(p.sort_results + (size_t)__float_as_uint(tag.x) * (size_t)p.LK + __float_as_uint(tag.w),
                        make_float4(a * lv.fW * gx, a * lv.fH * gy, a * lv.fD * gz, da));
             }
@@ -435,7 +443,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 // corners outside the level collect finite garbage that flush() never sends (same run, same corners)
-                const float aw = a * ((wx[n & 1] * wy[(n >> 1) & 1]) * wz[n >> 2]);
+                const float aw = a * w[n];
 #pragma unroll
                 for (int c = 0; c < 8; c += 2) ffma2(acc[n][c], acc[n][c + 1], aw, aw, god[c], god[c + 1]);
             }
