@@ -465,6 +465,7 @@ def run_ours(args, cfg):
     L = len(cfg["shapes"])
     # which backward the library takes for this rank's rows (it works batch element by batch element under the reducer)
     bwd_path = capi.backward_path(value_local[:1] if use_peer else value_local, packed[:1] if use_peer else packed, K)
+    fwd_heads = capi.forward_head_group(value_local, packed, K)   # heads per group of the forward's row order
     grad_value = accum = scratch = accum_heads = None
     if not use_peer:
         n_scratch = capi.scratch_bytes(value_local, packed, K)
@@ -669,7 +670,8 @@ def run_ours(args, cfg):
         "dram_frac": (traffic / (bwd_ms * 1e-3) / 1e9 / peak) if traffic else None,
         "peak_source": peak_src, "algorithmic_bytes_per_launch": bm["bwd_kernel"], "ms_per_launch": bwd_ms,
         "fwd_kernel": {"achieved": bm["fwd"] / (fwd_ms * 1e-3) / 1e9, "frac": bm["fwd"] / (fwd_ms * 1e-3) / 1e9 / peak,
-                       "algorithmic_bytes_per_launch": bm["fwd"], "ms_per_launch": fwd_ms},
+                       "algorithmic_bytes_per_launch": bm["fwd"], "ms_per_launch": fwd_ms,
+                       "row_order": ("query by query" if fwd_heads >= Gr else f"head groups of {fwd_heads} (value rows of a group stay in L2)")},
         "whole_step": {"achieved": bm["fwd_bwd"] / (ms_per_step * 1e-3) / 1e9,
                        "frac": bm["fwd_bwd"] / (ms_per_step * 1e-3) / 1e9 / peak,
                        "frac_of_nominal_8TBs": bm["fwd_bwd"] / (ms_per_step * 1e-3) / 8e12},

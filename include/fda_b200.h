@@ -121,6 +121,15 @@ size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int h
  */
 size_t fda_backward_sorted_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
                                          int num_points, int value_dtype);
+
+/*
+ * Heads per group of the forward's row order for this problem: num_heads = plain row order (query by query); a smaller
+ * divisor of num_heads = the grid walks all queries for that many heads at a time, so that the value rows it gathers stay
+ * L2-resident (chosen when one batch element's value volume exceeds the L2 budget and the call is large;
+ * FDA_FWD_HEAD_GROUPS).  Outputs do not depend on it.  Diagnostic; no counterpart in the reference.
+ */
+int fda_forward_head_group(int num_value, int num_heads, int head_dim, int num_levels, int num_query, int num_points,
+                           int value_dtype);
 int fda_backward_path(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query, int num_points,
                       int value_dtype);
 

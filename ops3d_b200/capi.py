@@ -16,7 +16,7 @@ DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 EXPORTS = (
     "fda_status_string", "fda_last_cuda_error", "fda_version", "fda_forward",
-    "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward_sorted_scratch_bytes", "fda_backward_path", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
+    "fda_backward_workspace_bytes", "fda_backward_scratch_bytes", "fda_backward_sorted_scratch_bytes", "fda_backward_path", "fda_forward_head_group", "fda_backward", "fda_backward_accumulate", "fda_cast_grad_value",
     "fda_backward_noalloc", "fda_peer_reduce_cast", "fda_multimem_reduce_cast", "fda_backward_accumulate_levels",
     "fda_peer_push_partials", "fda_peer_reduce_staged_cast", "fda_backward_bin_plan", "fda_backward_binned_part",
     "fda_pack_sampling", "fda_pack_sampling_backward", "fda_dcnv4_forward", "fda_dcnv4_backward",
@@ -178,6 +178,15 @@ def binning_applies(value, packed, K) -> bool:
     """True when the slab-binned path handles the largest level of this problem (given scratch)."""
     B, N, G, D = value.shape
     return int(load().fda_backward_scratch_bytes(B, N, G, D, _levels(packed, K), packed.shape[1], K, 0)) > 0
+
+
+def forward_head_group(value, packed, K) -> int:
+    """Heads per group of the forward's row order (``G``: plain row order)."""
+    B, N, G, D = value.shape
+    lib = load()
+    lib.fda_forward_head_group.argtypes = [ctypes.c_int] * 7
+    lib.fda_forward_head_group.restype = ctypes.c_int
+    return int(lib.fda_forward_head_group(N, G, D, _levels(packed, K), packed.shape[1], K, DTYPE_CODE[value.dtype]))
 
 
 def backward_path(value, packed, K) -> int:

@@ -520,6 +520,13 @@ size_t fda_backward_scratch_bytes(int batch, int num_value, int num_heads, int h
            dalpha_plane_bytes(batch, num_heads, num_levels, num_query, num_points, packed_dtype);
 }
 
+int fda_forward_head_group(int num_value, int num_heads, int head_dim, int num_levels, int num_query, int num_points,
+                           int value_dtype) {
+    if (num_value <= 0 || num_heads <= 0 || head_dim <= 0 || num_levels <= 0 || num_query <= 0 || num_points <= 0) return 0;
+    const Shape s{1, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, FDA_DTYPE_F32};
+    return forward_head_group(make_problem(s));
+}
+
 size_t fda_backward_sorted_scratch_bytes(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
                                          int num_points, int value_dtype) {
     return sort_layout(batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype).total;

@@ -111,6 +111,11 @@ def test_cell_sorted_path_selection_and_scratch_size():
     assert lib.fda_backward_path(B, N, G, D, L, Q // 16, K, 2) == 1
     assert lib.fda_backward_sorted_scratch_bytes(1, 288, 4, 32, 2, 288, 4, 2) == 0   # a few thousand points: too small
     assert lib.fda_backward_path(1, 288, 4, 32, 2, 288, 4, 2) == 0
+    # forward row order: head groups of 2 when 8 heads x 598016 cells x 64 B exceed the L2 budget and the call is large
+    assert lib.fda_forward_head_group(N, G, D, L, Q, K, 2) == 2
+    assert lib.fda_forward_head_group(N, 2, D, L, Q, K, 2) == 2        # a rank's 2-head slice fits: plain order (= all its heads)
+    assert lib.fda_forward_head_group(N, G, D, L, 1000, K, 2) == G     # small call: plain row order
+    assert lib.fda_forward_head_group(4608, G, D, 2, 4608, 4, 2) == G  # volume fits L2: plain row order
     # one rank of a head-split job at 8 GPUs: one batch element, 2 heads, every query -- as dense as the whole problem
     assert lib.fda_backward_path(1, N, 2, D, L, Q, K, 2) == 2
 
