@@ -63,6 +63,8 @@ def load() -> ctypes.CDLL:
     lib.fda_backward_scratch_bytes.argtypes = [i] * 8
     lib.fda_backward_path.argtypes = [i] * 8
     lib.fda_backward_path.restype = i
+    lib.fda_forward_head_group.argtypes = [i] * 7
+    lib.fda_forward_head_group.restype = i
     lib.fda_backward_sorted_scratch_bytes.argtypes = [i] * 8
     lib.fda_backward_sorted_scratch_bytes.restype = sz
     lib.fda_reload_config.restype = None
@@ -183,10 +185,7 @@ def binning_applies(value, packed, K) -> bool:
 def forward_head_group(value, packed, K) -> int:
     """Heads per group of the forward's row order (``G``: plain row order)."""
     B, N, G, D = value.shape
-    lib = load()
-    lib.fda_forward_head_group.argtypes = [ctypes.c_int] * 7
-    lib.fda_forward_head_group.restype = ctypes.c_int
-    return int(lib.fda_forward_head_group(N, G, D, _levels(packed, K), packed.shape[1], K, DTYPE_CODE[value.dtype]))
+    return int(load().fda_forward_head_group(N, G, D, _levels(packed, K), packed.shape[1], K, DTYPE_CODE[value.dtype]))
 
 
 def backward_path(value, packed, K) -> int:

@@ -12,9 +12,11 @@
                                                on a single GPU, or under torch.distributed.run on several:
         python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
             --master-port P -m ops3d_b200.microbench exchange
+    python -m ops3d_b200.microbench headpush   the head-sharded exchange (fda_head_slice_push_kernel): a compact fp32 image of
+                                               2 of 8 heads converted and stored into the full gradient, a world of one
 
 Sizes default to one rank's share of the largest benchmark configuration (256x512x2048 tile at strides
-8/16/32, G=8, D=32, K=8); ``--mb`` sets the image size of ``cast`` / ``exchange``.  Each prints one JSON line.
+8/16/32, G=8, D=32, K=8); ``--mb`` sets the image size of ``cast`` / ``exchange`` / ``headpush``.  Each prints one JSON line.
 """
 from __future__ import annotations
 
