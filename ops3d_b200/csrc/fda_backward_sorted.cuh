@@ -232,6 +232,10 @@ __global__ void __launch_bounds__(kScanThreads) fda_scan_apply_kernel(unsigned i
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((unsigned int)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
+// the same through L2 only: for rows that are read once (they would only push re-used rows out of L1)
+__device__ __forceinline__ void cp_async16_once(void *smem, const void *gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned int)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int kPending> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
@@ -357,7 +361,7 @@ __global__ void __launch_bounds__(kBlock, kMinBlocks) fda_sorted_walk_kernel(con
             if (t < tn) {
                 const float4 tag = ent_g[2 * t + 1];
                 uint4 *slot = ring + (size_t)((t % (unsigned int)kAhead) * kWalkSlot) * blockDim.x;
-                cp_async16(slot, go_base + (size_t)__float_as_uint(tag.x) * (size_t)p.D);
+                cp_async16_once(slot, go_base + (size_t)__float_as_uint(tag.x) * (size_t)p.D);
                 const unsigned int meta = __float_as_uint(tag.y), off0 = __float_as_uint(tag.z);
                 bool starts = t == 0;
                 if (!starts) {
