@@ -466,6 +466,8 @@ def run_ours(args, cfg):
     # which backward the library takes for this rank's rows (it works batch element by batch element under the reducer)
     bwd_path = capi.backward_path(value_local[:1] if use_peer else value_local, packed[:1] if use_peer else packed, K)
     fwd_heads = capi.forward_head_group(value_local, packed, K)   # heads per group of the forward's row order
+    # a step on one GPU follows fda_backward's own choice between the dense and the sparse handling of the fp32 image
+    touched = world == 1 and vdt != torch.float32 and capi.backward_touched_rows(value_local, packed, K)
     grad_value = accum = scratch = accum_heads = None
     if not use_peer:
         n_scratch = capi.scratch_bytes(value_local, packed, K)
@@ -491,16 +493,18 @@ def run_ours(args, cfg):
                                             0, L, capi.BWD_ZERO_IMAGE | capi.BWD_FINALIZE, scratch=scratch)
             accum[part.b_begin:part.b_end, :, part.h_begin:part.h_end] = accum_heads
             return
+        zero = 0 if world > 1 else (capi.BWD_ZERO_TOUCHED if touched else capi.BWD_ZERO_IMAGE)
         capi.backward_accumulate_levels(value_local, shapes, lsi, packed, grad_out, K, accum[part.b_begin:part.b_end],
-                                        grad_packed, 0, L, (0 if world > 1 else capi.BWD_ZERO_IMAGE) | capi.BWD_FINALIZE,
-                                        scratch=scratch)
+                                        grad_packed, 0, L, zero | capi.BWD_FINALIZE, scratch=scratch)
 
     def phase_tail():
         if use_peer:
             return
         if world > 1:
             dist.all_reduce(accum)
-        if accum is not grad_value:
+        if touched:
+            capi.cast_grad_value_touched(accum, grad_value, shapes, lsi, packed, K)
+        elif accum is not grad_value:
             capi.cast_grad_value(accum, grad_value)
 
     phases = [phase_forward, phase_backward, phase_tail]
@@ -657,7 +661,8 @@ def run_ours(args, cfg):
                             else (None, "captured for the full single-GPU launch only"))
     roofline = {
         "bound": "hbm",
-        "kernel": "backward pass (one C-ABI call) = zero-fill + " + {
+        "kernel": "backward pass (one C-ABI call) = " + ("fda_touch_rows_kernel (zeroes the image rows the points touch) + "
+                                                         if touched else "zero-fill + ") + {
             2: "cell sort (fda_sort_pass_kernel count / fill, fda_scan_*) + fda_sorted_walk_kernel + fda_sort_finalize_kernel",
             1: "slab binning + fda_backward_binned_kernel + fda_backward_kernel",
             0: "fda_backward_kernel"}[bwd_path],
@@ -694,6 +699,8 @@ def run_ours(args, cfg):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "ms_per_step_median": step_median, "ms_per_step_min": step_min,   # rank 0's own steps
             "ms_fwd": fwd_ms, "ms_bwd_kernel": bwd_ms, "ms_reduce_and_cast": tail_ms,
+            "grad_image": ("touched rows only (zeroed and converted from the point list)" if touched
+                           else "none (fp32 value accumulates in grad_value)" if vdt == torch.float32 else "dense zero-fill and cast"),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 value / f32 offsets, f32 accumulate" if cfg["vdt"] == "bfloat16" else "f32",
             "data": "synthetic", "config": config_block(cfg), "sharding": sharding,

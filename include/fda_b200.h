@@ -206,6 +206,7 @@ int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_element
 #define FDA_BWD_RESUME 2
 #define FDA_BWD_FINALIZE 4
 #define FDA_BWD_BINNED_DONE 8 /* the largest level was already scattered with fda_backward_binned_part */
+#define FDA_BWD_ZERO_TOUCHED 16 /* in place of FDA_BWD_ZERO_IMAGE: zero only the rows that points touch (see below) */
 int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
                                    const void *sampling_loc_attn, const void *grad_output,
                                    float *accum, void *grad_sampling_loc_attn,
@@ -213,6 +214,31 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
                                    int num_query, int num_points, int value_dtype, int packed_dtype,
                                    int im2col_step, int level_begin, int level_end, int flags,
                                    void *scratch, size_t scratch_bytes, void *stream);
+
+/*
+ * Sparse handling of the fp32 image, for calls whose sampling points reach only a part of the value
+ * volume (a few hundred queries looking into a large volume).  FDA_BWD_ZERO_TOUCHED on the first
+ * launch of a sequence zeroes, from the point list, exactly the image rows that the scatter can
+ * touch -- the 8 corner cells of every point of every level, one head row each -- and leaves the
+ * rest of the image as it is (it may hold anything).  Such an image must not be converted with
+ * fda_cast_grad_value, which reads all of it; fda_cast_grad_value_touched zero-fills grad_value and
+ * converts the same rows from the same point list.  With an fp32 value (image == grad_value) the
+ * flag acts as FDA_BWD_ZERO_IMAGE, and fda_cast_grad_value_touched returns FDA_ERR_BAD_DTYPE.
+ * fda_backward_touched_rows returns 1 when fda_backward itself works this way for a problem
+ * (FDA_BWD_TOUCHED: 0 never, 1 when the points can touch at most 60 % of the image -- 8 corner rows
+ * per point against num_value rows per head --, 2 always; never for a problem that
+ * fda_backward_path sends down the cell-sorted path), so that a caller composing the backward
+ * from the entry points above can follow the same rule.  The scatter adds the same terms to the same
+ * zeros either way.
+ * No counterpart in the reference (its grad_value is a zero-filled tensor in the value dtype that
+ * the kernel adds to, csrc/cuda/flash_deform_attn_cuda.cu:145).
+ */
+int fda_backward_touched_rows(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
+                              int num_points, int value_dtype);
+int fda_cast_grad_value_touched(const float *accum, void *grad_value, const int64_t *spatial_shapes,
+                                const int64_t *level_start_index, const void *sampling_loc_attn,
+                                int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                                int num_query, int num_points, int value_dtype, int packed_dtype, void *stream);
 
 /*
  * The slab-binned scatter of the largest level in `parts` launches, so that a multi-GPU caller can

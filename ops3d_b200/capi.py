@@ -22,8 +22,9 @@ EXPORTS = (
     "fda_pack_sampling", "fda_pack_sampling_backward", "fda_dcnv4_forward", "fda_dcnv4_backward",
     "fda_dcnv4_backward_workspace_bytes", "fda_dcnv4_output_size", "fda_roi_align3d_forward", "fda_roi_align3d_backward",
     "fda_nms3d", "fda_nms3d_workspace_bytes", "fda_reload_config", "fda_group_reduce_cast", "fda_head_slice_cast_push",
+    "fda_backward_touched_rows", "fda_cast_grad_value_touched",
 )
-BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE = 1, 2, 4, 8
+BWD_ZERO_IMAGE, BWD_RESUME, BWD_FINALIZE, BWD_BINNED_DONE, BWD_ZERO_TOUCHED = 1, 2, 4, 8, 16
 NOALLOC_MAX_ELEMENTS = 16 * 1024 * 1024
 
 _lib = None
@@ -68,6 +69,10 @@ def load() -> ctypes.CDLL:
     lib.fda_backward_sorted_scratch_bytes.argtypes = [i] * 8
     lib.fda_backward_sorted_scratch_bytes.restype = sz
     lib.fda_reload_config.restype = None
+    lib.fda_backward_touched_rows.argtypes = [i] * 8
+    lib.fda_backward_touched_rows.restype = i
+    lib.fda_cast_grad_value_touched.argtypes = [vp] * 5 + [i] * 9 + [vp]
+    lib.fda_cast_grad_value_touched.restype = i
     lib.fda_group_reduce_cast.argtypes = [vp, i, i, vp, i, i, sz, i, vp]
     lib.fda_group_reduce_cast.restype = i
     lib.fda_head_slice_cast_push.argtypes = [vp, vp, i, i, sz, sz, i, i, i, i, vp]
@@ -194,6 +199,12 @@ def backward_path(value, packed, K) -> int:
     return int(load().fda_backward_path(B, N, G, D, _levels(packed, K), packed.shape[1], K, DTYPE_CODE[value.dtype]))
 
 
+def backward_touched_rows(value, packed, K) -> bool:
+    """True when ``fda_backward`` zero-fills and converts only the image rows that sampling points touch."""
+    B, N, G, D = value.shape
+    return bool(load().fda_backward_touched_rows(B, N, G, D, _levels(packed, K), packed.shape[1], K, DTYPE_CODE[value.dtype]))
+
+
 def _scatter_launches(value, packed, K, first=True, last=True) -> int:
     """Kernels of one scatter call that was given scratch: sorted = (count, 3 x scan, fill on the first launch of a
     sequence) + walk (+ finalize on the last); binned = count, scan, fill, binned + plain; else the plain kernel."""
@@ -222,8 +233,10 @@ def backward(value, shapes, lsi, packed, grad_out, K, im2col_step=64, grad_value
             workspace.numel() * workspace.element_size() if workspace is not None else 0,
             B, N, G, D, L, Q, K, DTYPE_CODE[value.dtype], DTYPE_CODE[packed.dtype],
             im2col_step, 1, 0, _stream(value)))
-    # scatter kernels (the workspace includes the scratch of the binned / sorted path when one applies) + cast
-    _count(_scatter_launches(value, packed, K) + (1 if value.dtype != torch.float32 else 0))
+    # scatter kernels (the workspace includes the scratch of the binned / sorted path when one applies) + cast;
+    # the sparse image handling adds the pass that zeroes the touched rows
+    _count(_scatter_launches(value, packed, K) + (1 if value.dtype != torch.float32 else 0)
+           + (1 if backward_touched_rows(value, packed, K) else 0))
     return grad_value, grad_packed
 
 
@@ -254,6 +267,8 @@ def backward_accumulate_levels(value, shapes, lsi, packed, grad_out, K, accum, g
             level_begin, level_end, flags,
             scratch.data_ptr() if scratch is not None else None,
             scratch.numel() * scratch.element_size() if scratch is not None else 0, _stream(value)))
+    if (flags & BWD_ZERO_TOUCHED) and not (flags & BWD_ZERO_IMAGE) and value.dtype != torch.float32:
+        _count(1)
     if scratch is None or (flags & BWD_BINNED_DONE):
         _count(1)
     else:
@@ -291,6 +306,19 @@ def cast_grad_value(accum, grad_value):
         check(load().fda_cast_grad_value(accum.data_ptr(), grad_value.data_ptr(), accum.numel(),
                                          DTYPE_CODE[grad_value.dtype], _stream(accum)))
     _count(1 if grad_value.dtype != torch.float32 else 0)
+    return grad_value
+
+
+def cast_grad_value_touched(accum, grad_value, shapes, lsi, packed, K):
+    """``fda_cast_grad_value_touched``: zero-fills ``grad_value`` and converts the image rows that the sampling points
+    of ``packed`` touch (the counterpart of ``BWD_ZERO_TOUCHED``)."""
+    B, N, G, D = grad_value.shape
+    with torch.cuda.device(accum.device):
+        check(load().fda_cast_grad_value_touched(
+            accum.data_ptr(), grad_value.data_ptr(), shapes.data_ptr(), lsi.data_ptr(), packed.data_ptr(),
+            B, N, G, D, shapes.shape[0], packed.shape[1], K, DTYPE_CODE[grad_value.dtype], DTYPE_CODE[packed.dtype],
+            _stream(accum)))
+    _count(1)
     return grad_value
 
 

@@ -14,6 +14,7 @@
 #include "fda_backward.cuh"
 #include "fda_backward_binned.cuh"
 #include "fda_backward_sorted.cuh"
+#include "fda_backward_touched.cuh"
 #include "fda_config.h"
 #include "fda_forward.cuh"
 
@@ -64,6 +65,7 @@ fda::Config read_config() {
     c.sorted = 1;
     c.sort_seg = 32;
     c.sort_grid_x = 0;
+    c.touched = 1;
     c.sort_ahead = 2;  // 2 / 3 / 4 with 3 / 2 / 2 resident blocks: 31.2 / 33.8 / 33.5 ms per full-size backward
     if (const char *e = std::getenv("FDA_L2_KEEP_FRACTION")) c.l2_keep_fraction = std::atof(e);
     if (c.l2_keep_fraction < 0) c.l2_keep_fraction = 0;
@@ -89,6 +91,7 @@ fda::Config read_config() {
     if (const char *e = std::getenv("FDA_SORT_AHEAD")) c.sort_ahead = std::atoi(e);
     if (c.sort_ahead < 2) c.sort_ahead = 2;
     if (c.sort_ahead > 4) c.sort_ahead = 4;
+    if (const char *e = std::getenv("FDA_BWD_TOUCHED")) c.touched = std::atoi(e);
     return c;
 }
 
@@ -436,6 +439,35 @@ int launch_sorted(fda::Problem p, cudaStream_t st) {
     }
 }
 
+// Whether fda_backward zero-fills and converts only the rows of the fp32 image that sampling points touch
+// (fda_backward_touched.cuh) instead of the whole image.  Worst case (no two points share a row) the two point
+// passes write and read 8 rows of D floats per point; the dense passes move the image 2.5 times.  Taken when the
+// points can touch at most 60 % of the image.  The slab-binned scatter only adds to touched rows, like the plain
+// one; the cell-sorted path is for 10 and more points per cell and head and keeps the dense handling.
+bool touched_rows_choice(const Shape &s) {
+    if (s.vdt == FDA_DTYPE_F32 || g_config.touched <= 0) return false;
+    if (sort_layout(s.B, s.N, s.G, s.D, s.L, s.Q, s.K, s.vdt).total) return false;
+    if (g_config.touched >= 2) return true;
+    return (double)s.Q * s.L * s.K * 8.0 <= 0.6 * (double)s.N;
+}
+
+// kCast = false: zero the touched rows of p.accum; kCast = true: convert them into grad_value.
+template <typename VT, typename PT, bool kCast>
+int launch_touch_rows(const fda::Problem &p, void *grad_value, cudaStream_t st) {
+    if constexpr (std::is_same<VT, float>::value) {
+        (void)p; (void)grad_value; (void)st;
+        return FDA_ERR_BAD_DTYPE;
+    } else {
+        const int vecs = p.D / 4;
+        const unsigned long long total = (unsigned long long)p.B * p.rows_per_b * p.LK * vecs;
+        const unsigned long long blocks = (total + 255) / 256;
+        if (blocks > 0x7fffffffull) return FDA_ERR_BAD_SHAPE;
+        fda::fda_touch_rows_kernel<VT, PT, kCast><<<(unsigned)blocks, 256, 0, st>>>(p, static_cast<VT *>(grad_value), total, vecs);
+        const cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? FDA_OK : cuda_fail(e);
+    }
+}
+
 template <typename VT, typename PT>
 int launch_backward(fda::Problem p, cudaStream_t st) {
     if (p.sort_counters && !p.binned_elsewhere) return launch_sorted<VT, PT>(p, st);
@@ -565,7 +597,9 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
         !aligned16(grad_sampling_loc_attn))
         return FDA_ERR_MISALIGNED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (flags & FDA_BWD_ZERO_IMAGE) {
+    // an fp32 value accumulates in grad_value itself, which must be zero everywhere the points do not reach
+    const bool zero_touched = (flags & FDA_BWD_ZERO_TOUCHED) && value_dtype != FDA_DTYPE_F32;
+    if ((flags & FDA_BWD_ZERO_IMAGE) || ((flags & FDA_BWD_ZERO_TOUCHED) && !zero_touched)) {
         const size_t n = (size_t)batch * num_value * num_heads * head_dim;
         cudaError_t e = cudaMemsetAsync(accum, 0, n * sizeof(float), st);
         if (e != cudaSuccess) return cuda_fail(e);
@@ -573,6 +607,8 @@ int fda_backward_accumulate_levels(const void *value, const int64_t *spatial_sha
     fda::Problem p = make_problem(s);
     p.value = value; p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn;
     p.grad_out = grad_output; p.accum = accum; p.grad_packed = grad_sampling_loc_attn;
+    if (zero_touched && !(flags & FDA_BWD_ZERO_IMAGE))
+        if (int rc = FDA_DISPATCH(value_dtype, packed_dtype, (launch_touch_rows<VT, PT, false>(p, nullptr, st)))) return rc;
     p.level_mask = ((1 << level_end) - 1) & ~((1 << level_begin) - 1);
     p.resume = (flags & FDA_BWD_RESUME) ? 1 : 0;
     p.finalize = (flags & FDA_BWD_FINALIZE) ? 1 : 0;
@@ -664,6 +700,33 @@ int fda_cast_grad_value(const float *accum, void *grad_value, size_t num_element
     return e == cudaSuccess ? FDA_OK : cuda_fail(e);
 }
 
+int fda_backward_touched_rows(int batch, int num_value, int num_heads, int head_dim, int num_levels, int num_query,
+                              int num_points, int value_dtype) {
+    if (batch <= 0 || num_value <= 0 || num_heads <= 0 || head_dim <= 0 || num_levels <= 0 || num_query <= 0 || num_points <= 0)
+        return 0;
+    const Shape s{batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, FDA_DTYPE_F32};
+    return touched_rows_choice(s) ? 1 : 0;
+}
+
+int fda_cast_grad_value_touched(const float *accum, void *grad_value, const int64_t *spatial_shapes,
+                                const int64_t *level_start_index, const void *sampling_loc_attn,
+                                int batch, int num_value, int num_heads, int head_dim, int num_levels,
+                                int num_query, int num_points, int value_dtype, int packed_dtype, void *stream) {
+    if (!accum || !grad_value || !spatial_shapes || !level_start_index || !sampling_loc_attn) return FDA_ERR_NULL_POINTER;
+    const Shape s{batch, num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype, packed_dtype};
+    if (int rc = validate(s, batch)) return rc;
+    if (value_dtype == FDA_DTYPE_F32) return FDA_ERR_BAD_DTYPE;  // an fp32 value has no separate image
+    if (!aligned16(accum) || !aligned16(grad_value) || !aligned16(sampling_loc_attn)) return FDA_ERR_MISALIGNED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t n = (size_t)batch * num_value * num_heads * head_dim;
+    const cudaError_t e = cudaMemsetAsync(grad_value, 0, n * dtype_size(value_dtype), st);
+    if (e != cudaSuccess) return cuda_fail(e);
+    fda::Problem p = make_problem(s);
+    p.shapes = spatial_shapes; p.lsi = level_start_index; p.packed = sampling_loc_attn;
+    p.accum = const_cast<float *>(accum);
+    return FDA_DISPATCH(value_dtype, packed_dtype, (launch_touch_rows<VT, PT, true>(p, grad_value, st)));
+}
+
 int fda_backward(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
                  const void *sampling_loc_attn, const void *grad_output,
                  void *grad_value, void *grad_sampling_loc_attn,
@@ -682,12 +745,19 @@ int fda_backward(const void *value, const int64_t *spatial_shapes, const int64_t
     if (image_bytes > 0) accum = static_cast<float *>(workspace);
     void *scratch = need > image_bytes ? static_cast<char *>(workspace) + image_bytes : nullptr;
     if (!aligned16(grad_value)) return FDA_ERR_MISALIGNED;
+    const bool touched = image_bytes > 0 && fda_backward_touched_rows(batch, num_value, num_heads, head_dim, num_levels,
+                                                                      num_query, num_points, value_dtype);
     int rc = fda_backward_accumulate_levels(value, spatial_shapes, level_start_index, sampling_loc_attn, grad_output, accum,
                                             grad_sampling_loc_attn, batch, num_value, num_heads, head_dim, num_levels,
                                             num_query, num_points, value_dtype, packed_dtype, im2col_step, 0,
-                                            num_levels > 0 ? num_levels : 1, FDA_BWD_ZERO_IMAGE | FDA_BWD_FINALIZE,
+                                            num_levels > 0 ? num_levels : 1,
+                                            (touched ? FDA_BWD_ZERO_TOUCHED : FDA_BWD_ZERO_IMAGE) | FDA_BWD_FINALIZE,
                                             scratch, need - image_bytes, stream);
     if (rc != FDA_OK || image_bytes == 0) return rc;
+    if (touched)
+        return fda_cast_grad_value_touched(accum, grad_value, spatial_shapes, level_start_index, sampling_loc_attn, batch,
+                                           num_value, num_heads, head_dim, num_levels, num_query, num_points, value_dtype,
+                                           packed_dtype, stream);
     return fda_cast_grad_value(accum, grad_value, n, value_dtype, stream);
 }
 

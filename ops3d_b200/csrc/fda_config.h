@@ -16,6 +16,7 @@ struct Config {
     int sorted;               // FDA_BWD_SORT          cell-sorted backward: 0 off, 1 for large, dense problems, 2 whenever the shape allows (1)
     int sort_seg;             // FDA_SORT_SEGMENT      list entries per lane group between flushes (32)
     int sort_grid_x;          // FDA_SORT_GRID_X       blocks per batch element walking the sorted list (0 = fill the SMs once)
+    int touched;              // FDA_BWD_TOUCHED       fda_backward zero-fills / converts only the image rows the points touch: 0 never, 1 when they can touch at most 60 % of it, 2 always (1)
     int sort_ahead;           // FDA_SORT_AHEAD        points whose rows are in flight per lane of the walk: 2, 3 or 4 (2)
 };
 

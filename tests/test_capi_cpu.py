@@ -120,6 +120,31 @@ def test_cell_sorted_path_selection_and_scratch_size():
     assert lib.fda_backward_path(1, N, 2, D, L, Q, K, 2) == 2
 
 
+def test_sparse_image_handling_selection_and_validation(fda_env):
+    """When fda_backward zeroes and converts only the image rows that points touch: a pure host function of the shape
+    (8 corner rows per point against num_value rows per head: at most 60 % of the image)."""
+    lib = capi.load()
+    assert lib.fda_backward_touched_rows(4, 37376, 8, 32, 3, 200, 4, 2) == 1      # 200 object queries over 37 376 cells
+    assert lib.fda_backward_touched_rows(4, 37376, 8, 32, 3, 200, 4, 1) == 1      # fp16 too
+    assert lib.fda_backward_touched_rows(4, 37376, 8, 32, 3, 200, 4, 0) == 0      # fp32 accumulates in grad_value itself
+    assert lib.fda_backward_touched_rows(4, 37376, 8, 32, 3, 400, 4, 2) == 0      # twice the queries: dense is cheaper
+    assert lib.fda_backward_touched_rows(2, 4608, 8, 32, 2, 4608, 4, 2) == 0      # self-attention: every cell touched
+    assert lib.fda_backward_touched_rows(2, 598016, 8, 32, 3, 598016, 8, 2) == 0  # cell-sorted path
+    assert lib.fda_backward_touched_rows(2, 598016, 8, 32, 3, 100, 8, 2) == 1     # a 1.2 GB image for 100 queries
+    assert lib.fda_backward_touched_rows(0, 37376, 8, 32, 3, 200, 4, 2) == 0
+    fda_env(FDA_BWD_TOUCHED="0")
+    assert lib.fda_backward_touched_rows(4, 37376, 8, 32, 3, 200, 4, 2) == 0
+    fda_env(FDA_BWD_TOUCHED="2")
+    assert lib.fda_backward_touched_rows(2, 4608, 8, 32, 2, 4608, 4, 2) == 1
+    assert lib.fda_backward_touched_rows(2, 4608, 8, 32, 2, 4608, 4, 0) == 0
+    # the conversion validates on the host: null pointers, an fp32 value (no separate image), alignment
+    call = lambda a, g, pk, vdt: lib.fda_cast_grad_value_touched(a, g, 256, 256, pk, 1, 100, 2, 32, 1, 5, 4, vdt, 0, None)  # noqa: E731
+    assert call(None, 256, 256, 2) == 1
+    assert call(256, 256, None, 2) == 1
+    assert call(256, 256, 256, 0) == 2
+    assert call(256, 264, 256, 2) == 9
+
+
 def test_exchange_kernels_validate_before_launch():
     lib = capi.load()
     ptrs = (ctypes.c_void_p * 2)(256, 512)
