@@ -25,10 +25,6 @@ namespace fda {
 template <typename VT, typename PT, bool kCast>
 __global__ void __launch_bounds__(256) fda_touch_rows_kernel(const Problem p, VT *__restrict__ grad_value,
                                                              unsigned long long total_threads, int vecs) {
-    __shared__ LevelGeom geom[kMaxLevels];
-    if (threadIdx.x == 0)
-        build_level_table(geom, p.shapes, p.lsi, p.L, p.GD, p.value_elem_bytes, true, p.l2_keep_bytes);
-    __syncthreads();
     const unsigned long long t = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= total_threads) return;
     const unsigned long long point = t / (unsigned)vecs;
@@ -37,11 +33,20 @@ __global__ void __launch_bounds__(256) fda_touch_rows_kernel(const Problem p, VT
     const int i = (int)(point - row * (unsigned)p.LK);      // point of the row; its level is i / K
     const int b = (int)(row / (unsigned)p.rows_per_b);
     const int g = (int)(row % (unsigned)p.G);
-    const LevelGeom lv = geom[i >> (2 + p.k_shift)];
-
+    // Every thread reads its level's extents itself, side by side with the point's coordinates: one memory latency,
+    // where a level table built by one thread per block and a barrier cost more than the rest of this short kernel.
+    const int l = i >> (2 + p.k_shift);
     const PT *c = static_cast<const PT *>(p.packed) + row * (unsigned long long)(4 * p.LK) + 3 * i;
+    const float x = load1<PT>(c), y = load1<PT>(c + 1), z = load1<PT>(c + 2);
+    LevelGeom lv;
+    lv.D = (int)p.shapes[3 * l];
+    lv.H = (int)p.shapes[3 * l + 1];
+    lv.W = (int)p.shapes[3 * l + 2];
+    lv.start = (int)p.lsi[l];
+    lv.keep = 0;
+    lv.fD = (float)lv.D; lv.fH = (float)lv.H; lv.fW = (float)lv.W;
     PointGeom pg;
-    point_geometry(lv, p.GD, load1<PT>(c), load1<PT>(c + 1), load1<PT>(c + 2), pg);
+    point_geometry(lv, p.GD, x, y, z, pg);
 
     const size_t base = ((size_t)b * p.N + lv.start) * (size_t)p.GD + (size_t)g * p.D + (size_t)vec * 4;
     float *image = p.accum + base;
