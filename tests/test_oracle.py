@@ -161,3 +161,39 @@ def test_detection_oracles_match_reference_kernel_outputs():
     assert len(nms) >= 3
     for name, z in nms:
         assert o.nms3d(z["boxes"], z["scores"], float(z["threshold"])) == z["keep"].tolist(), name
+
+
+@pytest.mark.parametrize("coords", ["uniform", "clustered"])
+def test_grad_value_is_zero_outside_the_corner_rows_of_the_points(coords):
+    """The rule behind the sparse handling of the gradient image (zero and convert only the rows that points touch): the
+    oracle's grad_value is exactly zero in every head row that is not one of the 8 corner cells of some sampling point of
+    that head, with the corners taken as the kernels take them (voxel = ((2*loc - 1 + 1) * size - 1) / 2 rounded step by
+    step in fp32, floor, index inside the level)."""
+    import numpy as np
+
+    shapes = [(6, 7, 9), (3, 4, 5)]
+    B, Q, G, D, K = 2, 5, 3, 8, 4
+    value, sh, lsi, packed, grad_out = fda_oracle.make_inputs(shapes, B, Q, G, D, K, seed=47, coords=coords, lo=-0.2, hi=1.2)
+    _, gv, _ = fda_oracle.fused_forward_backward(value, sh, packed, grad_out, K)
+    L = len(shapes)
+    loc = packed[..., : 3 * L * K].reshape(B, Q, G, L, K, 3).numpy().astype(np.float32)
+    touched = np.zeros((B, value.shape[1], G), dtype=bool)
+    one, half = np.float32(1.0), np.float32(0.5)
+    for l, (Dz, H, W) in enumerate(shapes):
+        vox = []
+        for axis, size in ((0, W), (1, H), (2, Dz)):   # packed order is x, y, z
+            g = np.float32(2.0) * loc[:, :, :, l, :, axis] - one
+            vox.append(((g + one) * np.float32(size) - one) * half)
+        x0, y0, z0 = (np.floor(v).astype(np.int64) for v in vox)
+        b_idx, _, g_idx, _ = np.meshgrid(np.arange(B), np.arange(Q), np.arange(G), np.arange(K), indexing="ij")
+        for dz in (0, 1):
+            for dy in (0, 1):
+                for dx in (0, 1):
+                    x, y, z = x0 + dx, y0 + dy, z0 + dz
+                    ok = (x >= 0) & (x < W) & (y >= 0) & (y < H) & (z >= 0) & (z < Dz)
+                    cell = int(lsi[l]) + (z * H + y) * W + x
+                    touched[b_idx[ok], cell[ok], g_idx[ok]] = True
+    support = (gv != 0).any(dim=-1).numpy()
+    assert support.any() and not touched.all()
+    assert not (support & ~touched).any()
+    assert touched.sum() <= B * Q * G * L * K * 8
